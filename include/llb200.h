@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define LL_ABI_VERSION 11
+#define LL_ABI_VERSION 12
 
 #define LL_OK 0
 #define LL_ERR_ARG (-1)         /* bad shape / dtype / null pointer */
@@ -348,6 +348,81 @@ LL_API int ll_advance_pos(int32_t* pos, int cache_len, int max_pos, ll_stream st
  * Lets LLaMA.forward(idx, max_seq_length, input_pos) honour an arbitrary input_pos without a
  * host sync (ref: model.py:101-104 index_select by input_pos). */
 LL_API int ll_set_pos(int32_t* pos, const int64_t* input_pos, int cache_len, int max_pos, ll_stream stream);
+
+/* ---------------------------------------------------------------------------------------
+ * A residual stream kept in fp32 whatever the activation dtype (csrc/residual_ops.cu).
+ * ------------------------------------------------------------------------------------- */
+
+/* x[m][:] = wte[idx[m]][:] * scale in fp32; x_act (optional) the same in the activation dtype. */
+LL_API int ll_embed_scaled(const void* wte, int wte_dtype, const int64_t* idx, float scale, float* x, void* x_act,
+                           int act_dtype, int M, int dim, ll_stream stream);
+
+/* Norm on the sublayer's OUTPUT, with a one-number gain (a device scalar), then the residual sum:
+ *   r = x + gain * y / sqrt(mean(y^2) + eps)      (x == NULL: r is the normed y alone)
+ * r -> out (fp32, optional; may alias x, or be a slot of `stack`).  Then, optionally, the weighted sum over the outputs
+ * of all earlier layers:  v = mix_w[n_mix-1] * r + sum_{j < n_mix-1} mix_w[j] * stack[j * stack_stride + ...]
+ * (n_mix == 0: v = r).  v -> next (fp32, optional) and next_act (act_dtype, optional).  (y_dtype, act_dtype): both fp32,
+ * both bf16, or fp32 y with bf16 activations (the norm of the stream itself). */
+LL_API int ll_gain_norm_add_mix(const float* x, const void* y, int y_dtype, const float* gain, float eps, float* out,
+                                const float* stack, size_t stack_stride, const float* mix_w, int n_mix, float* next,
+                                void* next_act, int act_dtype, int rows, int dim, ll_stream stream);
+
+/* Clamped gated linear unit on the output gu [rows][gu_stride] of a GEMM over a stacked [gate; up] weight:
+ *   g = min(gu[c], limit), u = clamp(gu[ff + c], -limit, limit), h[c] = g * sigmoid(alpha * g) * (u + 1). */
+LL_API int ll_glu_clamp(const void* gu, int gu_stride, int ff, float limit, float alpha, void* h, int dtype, int rows,
+                        ll_stream stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Latent attention over a ring cache of latent rows (csrc/latent_attn.cu).  A cache row is
+ * [c (kv_rank) | k_rot (rot_dim)]; caches are [B][cache_len][kv_rank + rot_dim] in the activation dtype; the slot of
+ * position p is p % cache_len.  rope is [positions][rot_dims / 2][2] fp32 (cos, sin); rotation pairs dimension 2i with
+ * 2i + 1 on the first rot_dims (even, <= rot_dim) dimensions of the rotated part.  pos_ids [T] device int32: the
+ * positions of the step's tokens, the same for every sequence of the batch.
+ * ------------------------------------------------------------------------------------- */
+
+/* Row m = b * T + t of proj [B*T][proj_stride] holds at col0 the down-projection [kv_rank | rot_dim]:
+ * c = first part / sqrt(mean(first part^2) + eps) * norm_w (fp32 weights), k_rot = rotated second part -> cache row. */
+LL_API int ll_latent_kv_append(const void* proj, int dtype, int proj_stride, int col0, const float* norm_w, float eps,
+                               const float* rope, const int32_t* pos_ids, void* cache, int B, int T, int kv_rank,
+                               int rot_dim, int rot_dims, int cache_len, ll_stream stream);
+
+/* Attention in latent space.  q_lat (h, m, i) at q_lat[h * qs_h + m * qs_m + i]: the query with the key up-projection
+ * absorbed.  Head h's rotary query part (not yet rotated) is at proj[m][q_rot_col0 + h * q_head_stride ...], its gate
+ * logit at proj[m][gate_col0 + h] (gate_col0 < 0: none).  A query at position p sees p - window + 1 .. p (window <= 0: all).
+ *   out(h, m, :) = sigmoid(gate) * sum_j softmax_j((q_lat . c_j + rot(q_rot) . k_rot_j) * scale) c_j
+ * at out[h * os_h + m * os_m + i].  splits > 1 shares one query's keys among that many blocks (scratch of
+ * ll_latent_attn_scratch_bytes) and merges them in split order. */
+LL_API int ll_latent_attn(const void* q_lat, long long qs_h, long long qs_m, const void* proj, int proj_stride,
+                          int q_rot_col0, int q_head_stride, int gate_col0, const float* rope, const int32_t* pos_ids,
+                          const void* cache, void* out, long long os_h, long long os_m, int dtype, int B, int T, int n_head,
+                          int kv_rank, int rot_dim, int rot_dims, int cache_len, int window, float scale, int splits,
+                          float* scratch, ll_stream stream);
+LL_API size_t ll_latent_attn_scratch_bytes(int M, int n_head, int kv_rank, int splits);
+
+/* ---------------------------------------------------------------------------------------
+ * Mixture of experts (csrc/moe_ops.cu).  Nothing here synchronises with the host: counts, offsets and the
+ * permutation stay on the device.
+ * ------------------------------------------------------------------------------------- */
+
+/* Router: z = w_router [X][dim] (fp32) . x[m] + bias (fp32, optional); the `top` largest logits (ties: lowest index);
+ * expert_w = softmax over the chosen logits.  Also sorts the M * top (token, choice) pairs by expert:
+ * offsets [X + 1], perm [M * top] with perm[offsets[e] + r] = m * top + k.  counts [X], rank [M * top]: scratch. */
+LL_API int ll_moe_route(const void* x, int dtype, const float* w_router, const float* bias, int M, int dim, int n_experts,
+                        int top, int32_t* expert_idx, float* expert_w, int32_t* counts, int32_t* rank, int32_t* offsets,
+                        int32_t* perm, ll_stream stream);
+
+/* Grouped GEMM over the sorted rows, one expert's weight per row segment; w is the experts' stack.
+ * mode 1: w [X][2N][K] = [gate; up]; a [M][lda] read at token perm[r] / top;
+ *         c[r][:] = glu(a . gate^T, a . up^T) with ll_glu_clamp's formula, rows in sorted order.
+ * mode 0: w [X][N][K]; a [n_rows][lda] in sorted order; c[perm[r]][:] = a[r] . w[e]^T. */
+LL_API int ll_moe_grouped_gemm(const void* a, int lda, const void* w, const int32_t* offsets, const int32_t* perm, int mode,
+                               int dtype, int n_rows, int top, int n_experts, int N, int K, float limit, float alpha,
+                               void* c, int ldc, ll_stream stream);
+
+/* out[m] = sum_k expert_w[m][k] * y[m * top + k]  (+ sigmoid(shared_gate[m * gate_ld]) * shared_y[m], when shared_y is
+ * given; shared_gate NULL: the shared expert is added as it is). */
+LL_API int ll_moe_combine(const void* y, const float* expert_w, int top, const void* shared_y, int shared_ld,
+                          const void* shared_gate, int gate_ld, void* out, int dtype, int M, int dim, ll_stream stream);
 
 #ifdef __cplusplus
 }

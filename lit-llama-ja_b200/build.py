@@ -55,6 +55,37 @@ def build(force=False, verbose=False):
     return OUT
 
 
+def build_only(name, stems, verbose=False):
+    """A reduced library from the named sources only -> lit_llama/libllb200_<name>.so (select it with LLB200_LIB=<path>):
+    what a model family needs, without waiting for the kernels of the others.  Rebuilt only when a source is newer."""
+    out = HERE / "lit_llama" / f"libllb200_{name}.so"
+    srcs = [CSRC / f"{s}.cu" for s in stems]
+    deps = srcs + [CSRC / "common.cuh", HERE.parent / "include" / "llb200.h"]
+    if out.exists() and all(p.stat().st_mtime <= out.stat().st_mtime for p in deps):
+        return out
+    objdir = CSRC / f"_obj_{name}"
+    objdir.mkdir(exist_ok=True)
+    procs = []
+    for src in srcs:
+        obj = objdir / (src.stem + ".o")
+        cmd = [NVCC, *FLAGS, "-c", str(src), "-o", str(obj)]
+        procs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    objs, log = [], []
+    for src, obj, p in procs:
+        o, _ = p.communicate()
+        log.append(f"== {src.name}\n{o}")
+        if p.returncode != 0:
+            sys.stderr.write("\n".join(log))
+            raise RuntimeError(f"nvcc failed on {src.name}")
+        objs.append(str(obj))
+    tmp = out.with_suffix(f".{os.getpid()}.tmp")
+    subprocess.run([NVCC, "-shared", "-o", str(tmp), *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"], check=True)
+    os.replace(tmp, out)
+    if verbose:
+        print("\n".join(log))
+    return out
+
+
 def build_variant(name, defines, verbose=False):
     """Tuning build: the same sources with extra -D flags -> lit_llama/libllb200_<name>.so (select it at run time
     with LLB200_LIB=<path>; the default library is untouched)."""

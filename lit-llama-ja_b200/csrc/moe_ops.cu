@@ -1,0 +1,310 @@
+// Mixture-of-experts feed-forward: fp32 router with top-k selection, the sort of (token, choice)
+// pairs by expert entirely on the device (no host synchronisation: the step stays graph-capturable),
+// a grouped GEMM over the sorted rows whose blocks find their expert from the device-side counts,
+// and the weighted combination with an optional always-on shared expert.
+//
+//   route    z = W_r x + b (fp32), the `top` largest logits, weights = softmax over the chosen logits
+//   permute  rows sorted by expert: perm[offsets[e] + rank] = token * top + choice
+//   grouped  MODE_GLU : h[r][:] = glu(x[token(r)] . Wgu[e]^T)   (stacked [gate; up] weight, clamped GLU)
+//            MODE_DOWN: y[perm[r]][:] = h[r] . Wd[e]^T
+//   combine  out[m] = sum_k w[m][k] * y[m * top + k]  (+ sigmoid(s[m]) * shared[m])
+#include "common.cuh"
+
+namespace llb {
+
+constexpr int RT_TOK = 4;        // tokens per routing block
+constexpr int RT_THREADS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(RT_THREADS) moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w_router,
+                                                               const float* __restrict__ bias, int M, int dim, int X, int top,
+                                                               int32_t* __restrict__ expert_idx, float* __restrict__ expert_w,
+                                                               int32_t* __restrict__ counts, int32_t* __restrict__ rank) {
+  extern __shared__ float sm[];
+  float* xs = sm;                      // [RT_TOK][dim]
+  float* zs = xs + RT_TOK * dim;       // [RT_TOK][X]
+  const int m0 = blockIdx.x * RT_TOK;
+  const int nt = min(RT_TOK, M - m0);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int idx = tid; idx < nt * dim; idx += RT_THREADS) xs[idx] = dt<T>::ld(x, (size_t)m0 * dim + idx);
+  for (int idx = nt * dim + tid; idx < RT_TOK * dim; idx += RT_THREADS) xs[idx] = 0.f;
+  __syncthreads();
+  for (int e = warp; e < X; e += RT_THREADS / 32) {
+    const float* wr = w_router + (size_t)e * dim;
+    float a[RT_TOK];
+#pragma unroll
+    for (int t = 0; t < RT_TOK; ++t) a[t] = 0.f;
+    for (int i = lane; i < dim; i += 32) {
+      const float w = wr[i];
+#pragma unroll
+      for (int t = 0; t < RT_TOK; ++t) a[t] += w * xs[t * dim + i];
+    }
+#pragma unroll
+    for (int t = 0; t < RT_TOK; ++t) {
+      const float s = warp_sum(a[t]);
+      if (lane == 0) zs[t * X + e] = s + (bias ? bias[e] : 0.f);
+    }
+  }
+  __syncthreads();
+  if (warp < nt) {
+    float* z = zs + warp * X;
+    const int m = m0 + warp;
+    float v0 = 0.f, denom = 0.f;
+    for (int k = 0; k < top; ++k) {
+      float best = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int e = lane; e < X; e += 32) {
+        const float v = z[e];
+        if (v > best || (v == best && e < bi)) { best = v; bi = e; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+      }
+      if (k == 0) v0 = best;
+      const float p = expf(best - v0);
+      denom += p;
+      if (lane == 0) {
+        z[bi] = -INFINITY;
+        expert_idx[(size_t)m * top + k] = bi;
+        expert_w[(size_t)m * top + k] = p;                       // normalised below
+        rank[(size_t)m * top + k] = atomicAdd(&counts[bi], 1);
+      }
+      __syncwarp();
+    }
+    __syncwarp();
+    for (int k = lane; k < top; k += 32) expert_w[(size_t)m * top + k] /= denom;
+  }
+}
+
+__global__ void moe_permute_kernel(const int32_t* __restrict__ expert_idx, const int32_t* __restrict__ rank,
+                                   const int32_t* __restrict__ counts, int n_pairs, int X, int32_t* __restrict__ offsets,
+                                   int32_t* __restrict__ perm) {
+  extern __shared__ int32_t off[];   // [X + 1]
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < X; ++e) { off[e] = acc; acc += counts[e]; }
+    off[X] = acc;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0)
+    for (int e = threadIdx.x; e <= X; e += blockDim.x) offsets[e] = off[e];
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_pairs) perm[off[expert_idx[i]] + rank[i]] = i;
+}
+
+constexpr int GG_BN = 64, GG_BK = 16, GG_THREADS = 256;
+enum { MODE_DOWN = 0, MODE_GLU = 1 };
+
+// One block = a tile of 16*TM sorted rows of ONE expert x 64 output columns.  fp32 FMAs on operands
+// converted from T (exact for bf16), fp32 accumulation.
+template <typename T, int TM, int MODE>
+__global__ void __launch_bounds__(GG_THREADS) moe_grouped_gemm_kernel(const T* __restrict__ a, int lda, const T* __restrict__ w,
+                                                                      const int32_t* __restrict__ offsets,
+                                                                      const int32_t* __restrict__ perm, int top, int X, int N,
+                                                                      int K, float limit, float alpha, T* __restrict__ c, int ldc) {
+  constexpr int BM = 16 * TM;
+  constexpr int NB = MODE == MODE_GLU ? 2 : 1;
+  __shared__ float As[GG_BK][BM + 1];
+  __shared__ float Bs[NB][GG_BK][GG_BN + 1];
+  __shared__ int32_t src_row[BM], dst_row[BM];
+  __shared__ int s_e, s_r0, s_cnt;
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    int t = blockIdx.x, e = 0, found = -1;
+    for (; e < X; ++e) {
+      const int cnt = offsets[e + 1] - offsets[e];
+      const int tiles = (cnt + BM - 1) / BM;
+      if (t < tiles) { found = e; break; }
+      t -= tiles;
+    }
+    s_e = found;
+    if (found >= 0) {
+      s_r0 = offsets[found] + t * BM;
+      s_cnt = min(BM, offsets[found + 1] - s_r0);
+    }
+  }
+  __syncthreads();
+  if (s_e < 0) return;
+  const int e = s_e, r0 = s_r0, cnt = s_cnt;
+  const int n0 = blockIdx.y * GG_BN;
+  if (tid < BM) {
+    const int r = r0 + min(tid, cnt - 1);
+    const int pr = perm[r];
+    src_row[tid] = MODE == MODE_GLU ? pr / top : r;
+    dst_row[tid] = MODE == MODE_GLU ? r : pr;
+  }
+  __syncthreads();
+  const size_t rows_w = MODE == MODE_GLU ? 2 * (size_t)N : (size_t)N;   // rows of one expert's weight
+  const T* we = w + (size_t)e * rows_w * K;
+  const int tx = tid & 15, ty = tid >> 4;   // 16 x 16 threads: columns tx*4.., rows ty*TM..
+  float acc[NB][TM][4];
+#pragma unroll
+  for (int b = 0; b < NB; ++b)
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[b][i][j] = 0.f;
+
+  for (int k0 = 0; k0 < K; k0 += GG_BK) {
+    for (int idx = tid; idx < BM * GG_BK; idx += GG_THREADS) {
+      const int r = idx / GG_BK, kk = idx - r * GG_BK;
+      As[kk][r] = (k0 + kk < K) ? dt<T>::ld(a, (size_t)src_row[r] * lda + k0 + kk) : 0.f;
+    }
+    for (int idx = tid; idx < NB * GG_BN * GG_BK; idx += GG_THREADS) {
+      const int b = idx / (GG_BN * GG_BK), rem = idx - b * GG_BN * GG_BK;
+      const int n = rem / GG_BK, kk = rem - n * GG_BK;
+      const int col = n0 + n;
+      Bs[b][kk][n] = (col < N && k0 + kk < K) ? dt<T>::ld(we, ((size_t)b * N + col) * K + k0 + kk) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < GG_BK; ++kk) {
+      float av[TM];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) av[i] = As[kk][ty * TM + i];
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        float bv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) bv[j] = Bs[b][kk][tx * 4 + j];
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[b][i][j] += av[i] * bv[j];
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int r = ty * TM + i;
+    if (r >= cnt) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int col = n0 + tx * 4 + j;
+      if (col >= N) continue;
+      float v;
+      if (MODE == MODE_GLU) {
+        const float g = fminf(acc[0][i][j], limit);
+        const float u = fminf(fmaxf(acc[NB - 1][i][j], -limit), limit);
+        v = g / (1.f + expf(-alpha * g)) * (u + 1.f);
+      } else {
+        v = acc[0][i][j];
+      }
+      dt<T>::st(c, (size_t)dst_row[r] * ldc + col, v);
+    }
+  }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ y, const float* __restrict__ expert_w, int top,
+                                   const T* __restrict__ shared_y, int shared_ld, const T* __restrict__ shared_gate,
+                                   int gate_ld, T* __restrict__ out, int dim) {
+  const int m = blockIdx.x;
+  float sg = 0.f;
+  if (shared_y) sg = shared_gate ? 1.f / (1.f + expf(-dt<T>::ld(shared_gate, (size_t)m * gate_ld))) : 1.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float v = 0.f;
+    for (int k = 0; k < top; ++k) v += expert_w[(size_t)m * top + k] * dt<T>::ld(y, ((size_t)m * top + k) * dim + i);
+    if (shared_y) v += sg * dt<T>::ld(shared_y, (size_t)m * shared_ld + i);
+    dt<T>::st(out, (size_t)m * dim + i, v);
+  }
+}
+
+template <typename T, int TM, int MODE>
+static int launch_grouped(const void* a, int lda, const void* w, const int32_t* offsets, const int32_t* perm, int top, int X, int N,
+                          int K, float limit, float alpha, void* c, int ldc, int n_rows, cudaStream_t st) {
+  constexpr int BM = 16 * TM;
+  dim3 grid((n_rows + BM - 1) / BM + X, (N + GG_BN - 1) / GG_BN);
+  moe_grouped_gemm_kernel<T, TM, MODE><<<grid, GG_THREADS, 0, st>>>((const T*)a, lda, (const T*)w, offsets, perm, top, X, N, K, limit,
+                                                                   alpha, (T*)c, ldc);
+  LL_LAUNCH_OK("moe_grouped_gemm_kernel");
+  return LL_OK;
+}
+
+}  // namespace llb
+
+using namespace llb;
+
+extern "C" {
+
+int ll_moe_route(const void* x, int dtype, const float* w_router, const float* bias, int M, int dim, int n_experts, int top,
+                 int32_t* expert_idx, float* expert_w, int32_t* counts, int32_t* rank, int32_t* offsets, int32_t* perm,
+                 ll_stream stream) {
+  LL_CHECK_ARG(x && w_router && expert_idx && expert_w && counts && rank && offsets && perm, "moe_route: null pointer");
+  LL_CHECK_ARG(M >= 0 && dim > 0 && n_experts > 0 && top > 0 && top <= n_experts, "bad moe_route arguments");
+  if (M == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t smem = sizeof(float) * RT_TOK * ((size_t)dim + n_experts);
+  if (smem > 200 * 1024) {
+    set_error("moe_route: width %d with %d experts does not fit shared memory", dim, n_experts);
+    return LL_ERR_UNSUPPORTED;
+  }
+  LL_CUDA(cudaMemsetAsync(counts, 0, sizeof(int32_t) * n_experts, st));
+  const int blocks = (M + RT_TOK - 1) / RT_TOK;
+  if (dtype == LL_F32) {
+    LL_CUDA(cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    moe_route_kernel<float><<<blocks, RT_THREADS, smem, st>>>((const float*)x, w_router, bias, M, dim, n_experts, top, expert_idx,
+                                                             expert_w, counts, rank);
+  } else if (dtype == LL_BF16) {
+    LL_CUDA(cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    moe_route_kernel<__nv_bfloat16><<<blocks, RT_THREADS, smem, st>>>((const __nv_bfloat16*)x, w_router, bias, M, dim, n_experts, top,
+                                                                     expert_idx, expert_w, counts, rank);
+  } else {
+    set_error("moe_route: unsupported dtype %d", dtype);
+    return LL_ERR_UNSUPPORTED;
+  }
+  LL_LAUNCH_OK("moe_route_kernel");
+  const int n_pairs = M * top;
+  moe_permute_kernel<<<(n_pairs + 255) / 256, 256, sizeof(int32_t) * (n_experts + 1), st>>>(expert_idx, rank, counts, n_pairs,
+                                                                                          n_experts, offsets, perm);
+  LL_LAUNCH_OK("moe_permute_kernel");
+  return LL_OK;
+}
+
+int ll_moe_grouped_gemm(const void* a, int lda, const void* w, const int32_t* offsets, const int32_t* perm, int mode, int dtype,
+                        int n_rows, int top, int n_experts, int N, int K, float limit, float alpha, void* c, int ldc,
+                        ll_stream stream) {
+  LL_CHECK_ARG(a && w && offsets && perm && c, "moe_grouped_gemm: null pointer");
+  LL_CHECK_ARG(n_rows >= 0 && top > 0 && n_experts > 0 && N > 0 && K > 0 && lda >= K && ldc >= N && (mode == 0 || mode == 1),
+               "bad moe_grouped_gemm arguments");
+  if (n_rows == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool small = n_rows <= 16 * n_experts / 2 + 16;   // few rows per expert: narrow row tiles waste less
+#define LL_GG(T)                                                                                                              \
+  (mode == MODE_GLU ? (small ? launch_grouped<T, 1, MODE_GLU>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st)  \
+                             : launch_grouped<T, 4, MODE_GLU>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st)) \
+                    : (small ? launch_grouped<T, 1, MODE_DOWN>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st) \
+                             : launch_grouped<T, 4, MODE_DOWN>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st)))
+  if (dtype == LL_F32) return LL_GG(float);
+  if (dtype == LL_BF16) return LL_GG(__nv_bfloat16);
+#undef LL_GG
+  set_error("moe_grouped_gemm: unsupported dtype %d", dtype);
+  return LL_ERR_UNSUPPORTED;
+}
+
+int ll_moe_combine(const void* y, const float* expert_w, int top, const void* shared_y, int shared_ld, const void* shared_gate,
+                   int gate_ld, void* out, int dtype, int M, int dim, ll_stream stream) {
+  LL_CHECK_ARG(y && expert_w && out && top > 0 && M >= 0 && dim > 0, "bad moe_combine arguments");
+  if (M == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int threads = dim >= 1024 ? 256 : 128;
+  if (dtype == LL_F32)
+    moe_combine_kernel<float><<<M, threads, 0, st>>>((const float*)y, expert_w, top, (const float*)shared_y, shared_ld,
+                                                    (const float*)shared_gate, gate_ld, (float*)out, dim);
+  else if (dtype == LL_BF16)
+    moe_combine_kernel<__nv_bfloat16><<<M, threads, 0, st>>>((const __nv_bfloat16*)y, expert_w, top, (const __nv_bfloat16*)shared_y,
+                                                            shared_ld, (const __nv_bfloat16*)shared_gate, gate_ld,
+                                                            (__nv_bfloat16*)out, dim);
+  else {
+    set_error("moe_combine: unsupported dtype %d", dtype);
+    return LL_ERR_UNSUPPORTED;
+  }
+  LL_LAUNCH_OK("moe_combine_kernel");
+  return LL_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,159 @@
+// A residual stream kept in fp32 whatever the activation dtype: scaled embedding rows, the
+// "norm on the sublayer's output" update with a one-number RMSNorm gain, the weighted sum over
+// the outputs of all earlier layers (depth-weighted average), and the gated-linear-unit
+// activation with clamped pre-activations that the feed-forward layers of such models use.
+//
+// Every kernel takes the activation dtype as a template parameter (the GEMMs between these ops
+// read and write that dtype) and does its arithmetic in fp32.
+#include "common.cuh"
+
+namespace llb {
+
+// Block-wide sum of one float per thread (any blockDim.x that is a multiple of 32, up to 1024).
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+  if (w == 0) {
+    t = warp_sum(t);
+    if (lane == 0) red[0] = t;
+  }
+  __syncthreads();
+  t = red[0];
+  __syncthreads();
+  return t;
+}
+
+// x[m][:] = wte[idx[m]][:] * scale  (fp32), and the same rounded to the activation dtype.
+template <typename TW, typename TA>
+__global__ void embed_scaled_kernel(const TW* __restrict__ wte, const int64_t* __restrict__ idx, float scale,
+                                    float* __restrict__ x, TA* __restrict__ x_act, int dim) {
+  const int m = blockIdx.x;
+  const TW* row = wte + (size_t)idx[m] * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float v = dt<TW>::ld(row, i) * scale;
+    x[(size_t)m * dim + i] = v;
+    if (x_act) dt<TA>::st(x_act, (size_t)m * dim + i, v);
+  }
+}
+
+// r = x + gain * y / sqrt(mean(y^2) + eps)                      -> out      (fp32; may be a slot of `stack`)
+// n_mix > 0:  v = mix_w[n_mix-1] * r + sum_{j < n_mix-1} mix_w[j] * stack[j]   else v = r
+// v -> next (fp32, optional) and next_act (activation dtype, optional)
+// x == nullptr means a plain norm (r = gain * y / rms).
+template <typename TY, typename TA>
+__global__ void gain_norm_add_mix_kernel(const float* x, const TY* __restrict__ y,
+                                         const float* __restrict__ gain, float eps, float* out,
+                                         const float* stack, size_t stack_stride,
+                                         const float* __restrict__ mix_w, int n_mix, float* next,
+                                         TA* __restrict__ next_act, int dim) {
+  __shared__ float red[32];
+  const size_t base = (size_t)blockIdx.x * dim;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float v = dt<TY>::ld(y, base + i);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float k = gain[0] / sqrtf(ss / (float)dim + eps);
+  const float w_last = n_mix > 0 ? mix_w[n_mix - 1] : 1.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float r = dt<TY>::ld(y, base + i) * k;
+    if (x) r += x[base + i];
+    if (out) out[base + i] = r;
+    float v = r * w_last;
+    for (int j = 0; j < n_mix - 1; ++j) v += mix_w[j] * stack[(size_t)j * stack_stride + base + i];
+    if (next) next[base + i] = v;
+    if (next_act) dt<TA>::st(next_act, base + i, v);
+  }
+}
+
+// Gated linear unit with clamped pre-activations, on the output of one GEMM over the stacked
+// [gate; up] weight:  g = min(gu[m][c], limit), u = clamp(gu[m][ff + c], -limit, limit),
+// h[m][c] = g * sigmoid(alpha * g) * (u + 1).
+template <typename T>
+__global__ void glu_clamp_kernel(const T* __restrict__ gu, int gu_stride, int ff, float limit, float alpha,
+                                 T* __restrict__ h, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const size_t m = i / ff;
+  const int c = (int)(i - m * ff);
+  const float g = fminf(dt<T>::ld(gu, m * gu_stride + c), limit);
+  const float u = fminf(fmaxf(dt<T>::ld(gu, m * gu_stride + ff + c), -limit), limit);
+  dt<T>::st(h, i, g / (1.f + expf(-alpha * g)) * (u + 1.f));
+}
+
+}  // namespace llb
+
+using namespace llb;
+
+extern "C" {
+
+int ll_embed_scaled(const void* wte, int wte_dtype, const int64_t* idx, float scale, float* x, void* x_act,
+                    int act_dtype, int M, int dim, ll_stream stream) {
+  LL_CHECK_ARG(wte && idx && x && M >= 0 && dim > 0, "bad embed_scaled arguments");
+  if (M == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int threads = dim >= 1024 ? 256 : 128;
+  if (wte_dtype == LL_F32 && act_dtype == LL_F32)
+    embed_scaled_kernel<float, float><<<M, threads, 0, st>>>((const float*)wte, idx, scale, x, (float*)x_act, dim);
+  else if (wte_dtype == LL_BF16 && act_dtype == LL_BF16)
+    embed_scaled_kernel<__nv_bfloat16, __nv_bfloat16><<<M, threads, 0, st>>>((const __nv_bfloat16*)wte, idx, scale, x,
+                                                                            (__nv_bfloat16*)x_act, dim);
+  else if (wte_dtype == LL_BF16 && act_dtype == LL_F32)
+    embed_scaled_kernel<__nv_bfloat16, float><<<M, threads, 0, st>>>((const __nv_bfloat16*)wte, idx, scale, x, (float*)x_act, dim);
+  else {
+    set_error("embed_scaled: unsupported dtypes %d / %d", wte_dtype, act_dtype);
+    return LL_ERR_UNSUPPORTED;
+  }
+  LL_LAUNCH_OK("embed_scaled_kernel");
+  return LL_OK;
+}
+
+int ll_gain_norm_add_mix(const float* x, const void* y, int y_dtype, const float* gain, float eps, float* out,
+                         const float* stack, size_t stack_stride, const float* mix_w, int n_mix, float* next,
+                         void* next_act, int act_dtype, int rows, int dim, ll_stream stream) {
+  LL_CHECK_ARG(y && gain && rows >= 0 && dim > 0 && n_mix >= 0, "bad gain_norm_add_mix arguments");
+  LL_CHECK_ARG(n_mix <= 1 || (stack && mix_w), "gain_norm_add_mix: a mix needs the stack and its weights");
+  LL_CHECK_ARG(n_mix == 0 || mix_w, "gain_norm_add_mix: a mix needs its weights");
+  if (rows == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int threads = dim >= 2048 ? 512 : dim >= 512 ? 256 : 128;
+  if (y_dtype == LL_F32 && act_dtype == LL_F32)
+    gain_norm_add_mix_kernel<float, float><<<rows, threads, 0, st>>>(x, (const float*)y, gain, eps, out, stack, stack_stride,
+                                                                     mix_w, n_mix, next, (float*)next_act, dim);
+  else if (y_dtype == LL_BF16 && act_dtype == LL_BF16)
+    gain_norm_add_mix_kernel<__nv_bfloat16, __nv_bfloat16><<<rows, threads, 0, st>>>(
+        x, (const __nv_bfloat16*)y, gain, eps, out, stack, stack_stride, mix_w, n_mix, next, (__nv_bfloat16*)next_act, dim);
+  else if (y_dtype == LL_F32 && act_dtype == LL_BF16)
+    gain_norm_add_mix_kernel<float, __nv_bfloat16><<<rows, threads, 0, st>>>(x, (const float*)y, gain, eps, out, stack, stack_stride,
+                                                                             mix_w, n_mix, next, (__nv_bfloat16*)next_act, dim);
+  else {
+    set_error("gain_norm_add_mix: unsupported dtypes %d / %d", y_dtype, act_dtype);
+    return LL_ERR_UNSUPPORTED;
+  }
+  LL_LAUNCH_OK("gain_norm_add_mix_kernel");
+  return LL_OK;
+}
+
+int ll_glu_clamp(const void* gu, int gu_stride, int ff, float limit, float alpha, void* h, int dtype, int rows,
+                 ll_stream stream) {
+  LL_CHECK_ARG(gu && h && ff > 0 && gu_stride >= 2 * ff && rows >= 0, "bad glu_clamp arguments");
+  const size_t n = (size_t)rows * ff;
+  if (n == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (dtype == LL_F32) glu_clamp_kernel<float><<<blocks, 256, 0, st>>>((const float*)gu, gu_stride, ff, limit, alpha, (float*)h, n);
+  else if (dtype == LL_BF16)
+    glu_clamp_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)gu, gu_stride, ff, limit, alpha, (__nv_bfloat16*)h, n);
+  else {
+    set_error("glu_clamp: unsupported dtype %d", dtype);
+    return LL_ERR_UNSUPPORTED;
+  }
+  LL_LAUNCH_OK("glu_clamp_kernel");
+  return LL_OK;
+}
+
+}  // extern "C"

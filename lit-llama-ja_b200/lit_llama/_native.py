@@ -29,7 +29,7 @@ GEMV_ODD, GEMV_EVEN = 2, 4
 
 _DT = {torch.float32: LL_F32, torch.bfloat16: LL_BF16, torch.float16: LL_F16}
 
-vp, i32, sz_t = C.c_void_p, C.c_int, C.c_size_t
+vp, i32, i64, sz_t = C.c_void_p, C.c_int, C.c_longlong, C.c_size_t
 
 
 class GemvArgs(C.Structure):
@@ -50,7 +50,14 @@ class GemvArgs(C.Structure):
 
 
 def _proto(name, argtypes, restype=C.c_int):
-    fn = getattr(lib, name)
+    """Bind one export.  A reduced build of the library (build.py --only ...) lacks the kernels of the model families it
+    was not built for: their entries raise when called."""
+    try:
+        fn = getattr(lib, name)
+    except AttributeError:
+        def missing(*_a, _name=name):
+            raise RuntimeError(f"{_LIB_PATH.name} was built without {_name}; rebuild with lit-llama-ja_b200/build.py")
+        return missing
     fn.argtypes = argtypes
     fn.restype = restype
     return fn
@@ -100,10 +107,20 @@ EXPORTS = {
     "ll_advance_pos": ([vp, i32, i32, vp], C.c_int),
     "ll_set_pos": ([vp, vp, i32, i32, vp], C.c_int),
     "ll_apply_rope": ([vp, vp, vp, i32, i32, i32, i32, i32, vp], C.c_int),
+    "ll_embed_scaled": ([vp, i32, vp, C.c_float, vp, vp, i32, i32, i32, vp], C.c_int),
+    "ll_gain_norm_add_mix": ([vp, vp, i32, vp, C.c_float, vp, vp, sz_t, vp, i32, vp, vp, i32, i32, i32, vp], C.c_int),
+    "ll_glu_clamp": ([vp, i32, i32, C.c_float, C.c_float, vp, i32, i32, vp], C.c_int),
+    "ll_latent_kv_append": ([vp, i32, i32, i32, vp, C.c_float, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp], C.c_int),
+    "ll_latent_attn": ([vp, i64, i64, vp, i32, i32, i32, i32, vp, vp, vp, vp, i64, i64, i32, i32, i32, i32, i32, i32, i32, i32,
+                        i32, C.c_float, i32, vp, vp], C.c_int),
+    "ll_latent_attn_scratch_bytes": ([i32, i32, i32, i32], sz_t),
+    "ll_moe_route": ([vp, i32, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp], C.c_int),
+    "ll_moe_grouped_gemm": ([vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, C.c_float, C.c_float, vp, i32, vp], C.c_int),
+    "ll_moe_combine": ([vp, vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, vp], C.c_int),
 }
 _fn = {name: _proto(name, a, r) for name, (a, r) in EXPORTS.items()}
 
-ABI_VERSION = 11
+ABI_VERSION = 12
 if _fn["ll_abi_version"]() != ABI_VERSION:
     raise ImportError("libllb200.so ABI version mismatch; rebuild with lit-llama-ja_b200/build.py")
 

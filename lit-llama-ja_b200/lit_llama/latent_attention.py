@@ -1,0 +1,118 @@
+"""Latent attention: keys and values are up-projections of one low-rank row per token, plus one rotated key part that all
+heads share; only that row is cached.
+
+With h the mixer's input, per token
+    [q | g | d] = W_in h            q: heads x [nope_dim | rot_dim];  g: one gate logit per head;  d: [kv_rank | rot_dim]
+    c = rmsnorm(d[:kv_rank]) * w    k_rot = rope(d[kv_rank:])          -> the cache row [c | k_rot]
+    score(i, j, head) = (q_nope . (W_uk c_j) + rope(q_rot) . k_rot_j) * scale,   j in the sliding window of i
+    out = W_o concat_heads( sigmoid(g) * sum_j softmax_j(score) (W_uv c_j) )
+The kernels work in latent space: W_uk is absorbed into the query (q_lat = W_uk^T q_nope, a batched GEMM over heads) and
+W_uv is applied to the weighted sum of the c_j, so every head reads the same cache row once, in prefill and in decoding
+alike.  A layer built with ``kv_from`` has no down-projection: it reads another layer's rows with its own W_uk, W_uv,
+queries and window.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn as nn
+from torch.nn import functional as F
+
+from . import _native as N
+
+
+@dataclass
+class LatentAttentionSpec:
+    width: int
+    heads: int
+    nope_dim: int                 # un-rotated query / key dimensions per head
+    rot_dim: int                  # rotated dimensions per head (one key part for all heads)
+    v_dim: int
+    kv_rank: int
+    window: Optional[int]         # position i sees i - window + 1 .. i; None: everything before it
+    scale: float
+    rot_base: float = 10000.0
+    rot_dims: Optional[int] = None   # the first rot_dims of the rotated part turn, the rest pass; default all
+    eps: float = 1e-5
+    kv_from: Optional[int] = None    # index of the layer whose cache rows this layer reads
+
+    def __post_init__(self):
+        if self.rot_dims is None:
+            self.rot_dims = self.rot_dim
+        if self.rot_dims % 2 or not 0 <= self.rot_dims <= self.rot_dim:
+            raise ValueError(f"rot_dims {self.rot_dims} must be even and at most rot_dim {self.rot_dim}")
+
+    @property
+    def row(self) -> int:
+        return self.kv_rank + self.rot_dim
+
+    @property
+    def q_head(self) -> int:
+        return self.nope_dim + self.rot_dim
+
+
+def build_rope_table(n_pos: int, rot_dims: int, base: float, device) -> torch.Tensor:
+    """``[n_pos, rot_dims / 2, 2]`` fp32 (cos, sin) of ``pos * base^(-2i / rot_dims)``; angles formed in float64 so that the
+    table is exact to fp32 rounding at any position."""
+    i = torch.arange(rot_dims // 2, dtype=torch.float64)
+    freq = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / max(rot_dims, 1))
+    ang = torch.arange(n_pos, dtype=torch.float64)[:, None] * freq[None]
+    return torch.stack((ang.cos(), ang.sin()), dim=-1).float().contiguous().to(device)
+
+
+class LatentAttention(nn.Module):
+    def __init__(self, spec: LatentAttentionSpec, dtype: torch.dtype, device) -> None:
+        super().__init__()
+        s = self.spec = spec
+        self.owns_cache = s.kv_from is None
+        self.q_cols = s.heads * s.q_head
+        self.gate_col0 = self.q_cols
+        self.kv_col0 = self.q_cols + s.heads
+        n_in = self.kv_col0 + (s.row if self.owns_cache else 0)
+        kw = dict(dtype=dtype, device=device)
+        self.w_in = nn.Parameter(torch.empty((n_in, s.width), **kw), requires_grad=False)          # [W_q; W_g; W_dkv]
+        self.w_uk = nn.Parameter(torch.empty((s.heads, s.nope_dim, s.kv_rank), **kw), requires_grad=False)
+        self.w_uv_t = nn.Parameter(torch.empty((s.heads, s.kv_rank, s.v_dim), **kw), requires_grad=False)
+        self.w_o = nn.Parameter(torch.empty((s.width, s.heads * s.v_dim), **kw), requires_grad=False)
+        self.kv_norm = nn.Parameter(torch.ones(s.kv_rank, dtype=torch.float32, device=device), requires_grad=False) \
+            if self.owns_cache else None
+
+    def load(self, get) -> None:
+        """``get(suffix)`` returns the tensor '<layer>.mix.<suffix>' ([out, in] for the Linears)."""
+        s = self.spec
+        parts = [get("q"), get("g")] + ([get("dkv")] if self.owns_cache else [])
+        self.w_in.copy_(torch.cat([p.to(self.w_in.dtype) for p in parts], dim=0))
+        self.w_uk.copy_(get("uk").reshape(s.heads, s.nope_dim, s.kv_rank))
+        self.w_uv_t.copy_(get("uv").reshape(s.heads, s.v_dim, s.kv_rank).transpose(1, 2))
+        self.w_o.copy_(get("o"))
+        if self.owns_cache:
+            self.kv_norm.copy_(get("dkv.norm").float())
+
+    def forward(self, x_act: torch.Tensor, B: int, T: int, pos_ids: torch.Tensor, rope: torch.Tensor, cache: torch.Tensor,
+                splits: int = 1) -> torch.Tensor:
+        """x_act ``[B*T, width]`` -> ``[B*T, width]``; ``cache`` ``[B, S, row]`` is this layer's or its source's (already
+        appended to by the source in this step)."""
+        s = self.spec
+        M = B * T
+        dt = N.dtype_code(x_act.dtype)
+        st = N.stream()
+        proj = F.linear(x_act, self.w_in)                                     # [M, n_in]
+        S = cache.shape[1]
+        if self.owns_cache:
+            N.call("ll_latent_kv_append", N.ptr(proj), dt, proj.shape[1], self.kv_col0, N.ptr(self.kv_norm), float(s.eps),
+                   N.ptr(rope), N.ptr(pos_ids), N.ptr(cache), B, T, s.kv_rank, s.rot_dim, s.rot_dims, S, st)
+        q_nope = proj[:, : self.q_cols].view(M, s.heads, s.q_head)[:, :, : s.nope_dim].transpose(0, 1)   # [H, M, nope] view
+        q_lat = torch.bmm(q_nope, self.w_uk)                                  # [H, M, kv_rank]
+        o_lat = torch.empty_like(q_lat)
+        scratch = None
+        if splits > 1:
+            scratch = torch.empty(N.call_ret("ll_latent_attn_scratch_bytes", M, s.heads, s.kv_rank, splits) // 4,
+                                  dtype=torch.float32, device=x_act.device)
+        N.call("ll_latent_attn", N.ptr(q_lat), M * s.kv_rank, s.kv_rank, N.ptr(proj), proj.shape[1], s.nope_dim, s.q_head,
+               self.gate_col0, N.ptr(rope), N.ptr(pos_ids), N.ptr(cache), N.ptr(o_lat), M * s.kv_rank, s.kv_rank, dt, B, T,
+               s.heads, s.kv_rank, s.rot_dim, s.rot_dims, S, s.window if s.window is not None else 0, float(s.scale), splits,
+               N.ptr(scratch), st)
+        o = torch.bmm(o_lat, self.w_uv_t)                                     # [H, M, v_dim]
+        return F.linear(o.transpose(0, 1).reshape(M, s.heads * s.v_dim), self.w_o)

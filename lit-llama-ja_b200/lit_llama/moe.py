@@ -1,0 +1,115 @@
+"""Mixture-of-experts feed-forward with clamped gated-linear-unit experts and an optional always-on shared expert.
+
+    z = W_r h + b  (fp32)      the ``top`` largest logits choose the experts, weights = softmax over the chosen logits
+    expert(h) = W_down( g * sigmoid(alpha * g) * (u + 1) ),  g = min(W_gate h, limit),  u = clamp(W_up h, -limit, limit)
+    y = sum_k w_k expert_k(h)  +  sigmoid(w_sg . h) * shared(h)
+
+The experts' weights are stacked ([X, 2 ff, width] for [gate; up], [X, width, ff] for down) and run as two grouped GEMMs
+over the (token, choice) pairs sorted by expert; counts, offsets and the permutation never leave the device, so a step
+is one fixed launch sequence.  The shared expert is dense (library GEMMs) with its gate logit as one more output row.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn as nn
+from torch.nn import functional as F
+
+from . import _native as N
+
+
+@dataclass
+class MoESpec:
+    width: int
+    experts: int
+    top: int
+    ff: int
+    limit: float
+    shared_ff: Optional[int] = None      # None: no shared expert
+    shared_limit: Optional[float] = None
+    shared_gate: bool = True             # the shared expert is scaled by sigmoid(w_sg . h)
+    router_bias: bool = True
+    alpha: float = 1.702                 # slope inside the sigmoid of the gated unit
+
+
+def glu_clamp(gu: torch.Tensor, ff: int, limit: float, alpha: float) -> torch.Tensor:
+    """``gu [rows, >= 2 ff]`` (columns [gate | up | ...]) -> ``[rows, ff]``: the clamped gated unit of this module."""
+    out = torch.empty((gu.shape[0], ff), dtype=gu.dtype, device=gu.device)
+    N.call("ll_glu_clamp", N.ptr(gu), gu.stride(0), ff, float(limit), float(alpha), N.ptr(out), N.dtype_code(gu.dtype),
+           gu.shape[0], N.stream())
+    return out
+
+
+class MoE(nn.Module):
+    def __init__(self, spec: MoESpec, dtype: torch.dtype, device) -> None:
+        super().__init__()
+        s = self.spec = spec
+        if not 0 < s.top <= s.experts:
+            raise ValueError(f"top {s.top} of {s.experts} experts")
+        kw = dict(dtype=dtype, device=device)
+        f32 = dict(dtype=torch.float32, device=device)
+        self.w_router = nn.Parameter(torch.empty((s.experts, s.width), **f32), requires_grad=False)
+        self.b_router = nn.Parameter(torch.zeros(s.experts, **f32), requires_grad=False) if s.router_bias else None
+        self.w_gu = nn.Parameter(torch.empty((s.experts, 2 * s.ff, s.width), **kw), requires_grad=False)
+        self.w_down = nn.Parameter(torch.empty((s.experts, s.width, s.ff), **kw), requires_grad=False)
+        if s.shared_ff:
+            rows = 2 * s.shared_ff + (1 if s.shared_gate else 0)
+            self.w_shared_in = nn.Parameter(torch.empty((rows, s.width), **kw), requires_grad=False)   # [gate; up; sg]
+            self.w_shared_down = nn.Parameter(torch.empty((s.width, s.shared_ff), **kw), requires_grad=False)
+
+    def load(self, get) -> None:
+        """``get(suffix)`` returns the tensor '<layer>.mlp.<suffix>'."""
+        s = self.spec
+        self.w_router.copy_(get("router").float())
+        if self.b_router is not None:
+            self.b_router.copy_(get("router.b").float())
+        for e in range(s.experts):
+            self.w_gu[e, : s.ff].copy_(get(f"e{e}.gate"))
+            self.w_gu[e, s.ff:].copy_(get(f"e{e}.up"))
+            self.w_down[e].copy_(get(f"e{e}.down"))
+        if s.shared_ff:
+            f = s.shared_ff
+            self.w_shared_in[:f].copy_(get("shared.gate"))
+            self.w_shared_in[f:2 * f].copy_(get("shared.up"))
+            if s.shared_gate:
+                self.w_shared_in[2 * f:].copy_(get("shared.sg").reshape(1, s.width))
+            self.w_shared_down.copy_(get("shared.down"))
+
+    def route(self, x_act: torch.Tensor):
+        """(expert_idx [M, top] int32, expert_w [M, top] fp32, offsets [X + 1], perm [M * top])."""
+        s = self.spec
+        M, dev = x_act.shape[0], x_act.device
+        i32 = dict(dtype=torch.int32, device=dev)
+        idx = torch.empty((M, s.top), **i32)
+        w = torch.empty((M, s.top), dtype=torch.float32, device=dev)
+        counts, rank = torch.empty(s.experts, **i32), torch.empty(M * s.top, **i32)
+        offsets, perm = torch.empty(s.experts + 1, **i32), torch.empty(M * s.top, **i32)
+        N.call("ll_moe_route", N.ptr(x_act), N.dtype_code(x_act.dtype), N.ptr(self.w_router), N.ptr(self.b_router), M, s.width,
+               s.experts, s.top, N.ptr(idx), N.ptr(w), N.ptr(counts), N.ptr(rank), N.ptr(offsets), N.ptr(perm), N.stream())
+        return idx, w, offsets, perm
+
+    def forward(self, x_act: torch.Tensor) -> torch.Tensor:
+        s = self.spec
+        M, dev, dtype = x_act.shape[0], x_act.device, x_act.dtype
+        dt, st = N.dtype_code(dtype), N.stream()
+        _, w, offsets, perm = self.route(x_act)
+        n = M * s.top
+        h = torch.empty((n, s.ff), dtype=dtype, device=dev)
+        N.call("ll_moe_grouped_gemm", N.ptr(x_act), x_act.stride(0), N.ptr(self.w_gu), N.ptr(offsets), N.ptr(perm), 1, dt, n,
+               s.top, s.experts, s.ff, s.width, float(s.limit), float(s.alpha), N.ptr(h), s.ff, st)
+        y = torch.empty((n, s.width), dtype=dtype, device=dev)
+        N.call("ll_moe_grouped_gemm", N.ptr(h), s.ff, N.ptr(self.w_down), N.ptr(offsets), N.ptr(perm), 0, dt, n, s.top, s.experts,
+               s.width, s.ff, 0.0, 0.0, N.ptr(y), s.width, st)
+        ys = gate = None
+        gate_ld = 0
+        if s.shared_ff:
+            gu = F.linear(x_act, self.w_shared_in)
+            hs = glu_clamp(gu, s.shared_ff, s.shared_limit if s.shared_limit is not None else s.limit, s.alpha)
+            ys = F.linear(hs, self.w_shared_down)
+            if s.shared_gate:
+                gate, gate_ld = gu[:, 2 * s.shared_ff:], gu.stride(0)
+        out = torch.empty((M, s.width), dtype=dtype, device=dev)
+        N.call("ll_moe_combine", N.ptr(y), N.ptr(w), s.top, N.ptr(ys), s.width, N.ptr(gate), gate_ld, N.ptr(out), dt, M, s.width, st)
+        return out

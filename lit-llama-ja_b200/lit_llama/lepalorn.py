@@ -329,6 +329,8 @@ class Lepalorn(nn.Module):
             x = nxt
             if self.layer_probe is not None:
                 self.layer_probe(i, x)
+        if sel is not None and len(sel) == 0:      # the step only fills the cache
+            return torch.empty((B, 0, cfg.vocab), dtype=torch.float32, device=dev)
         if sel is not None:
             ridx = (torch.arange(B, device=dev)[:, None] * T + torch.tensor(sel, device=dev, dtype=torch.long)[None]).reshape(-1)
             x = x.index_select(0, ridx).contiguous()

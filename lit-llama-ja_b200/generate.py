@@ -104,6 +104,10 @@ def load_model(checkpoint_path: Path, quantize: Optional[str], device: torch.dev
     floating-point checkpoint inside ``load_state_dict``, tensor by tensor, from the lazy placeholders."""
     from lit_llama.utils import stream_load_state_dict
 
+    if Path(checkpoint_path).is_dir():     # a model folder (config.json + model.safetensors): the registry picks the class
+        from lit_llama.registry import load_model
+
+        return load_model(checkpoint_path, quantize, device, dtype)
     with lazy_load(checkpoint_path) as checkpoint:
         name = llama_model_lookup(checkpoint)
         with EmptyInitOnDevice(device=device, dtype=dtype, quantization_mode=quantize):
@@ -125,23 +129,32 @@ def main(
     checkpoint_path: Path = Path("checkpoints/lit-llama/7B/lit-llama.pth"),
     tokenizer_path: Path = Path("checkpoints/lit-llama/tokenizer.model"),
     quantize: Optional[str] = None,
+    prompt_ids: Optional[str] = None,
+    dtype: Optional[str] = None,
 ) -> None:
-    """ref: generate.py:92-155 - same flags and output."""
+    """ref: generate.py:92-155 - same flags and output.  ``checkpoint_path`` may also be a model folder (config.json +
+    model.safetensors, any registered architecture); ``prompt_ids`` ("5,17,3") feeds token ids directly and prints ids,
+    for models that come without a tokenizer."""
     checkpoint_path, tokenizer_path = Path(checkpoint_path), Path(tokenizer_path)
-    assert checkpoint_path.is_file(), checkpoint_path
-    assert tokenizer_path.is_file(), tokenizer_path
+    assert checkpoint_path.exists(), checkpoint_path
+    assert prompt_ids is not None or tokenizer_path.is_file(), tokenizer_path
     if not torch.cuda.is_available():
         raise RuntimeError("lit-llama-ja_b200 needs a CUDA device (sm_100a); there is no CPU fallback")
     device = torch.device("cuda", torch.cuda.current_device())
-    dtype = torch.bfloat16 if torch.cuda.is_bf16_supported() else torch.float32
+    dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype] if dtype else (
+        torch.bfloat16 if torch.cuda.is_bf16_supported() else torch.float32)
 
     print("Loading model ...", file=sys.stderr)
     t0 = time.time()
     model = load_model(checkpoint_path, quantize, device, dtype)
     print(f"Time to load model: {time.time() - t0:.02f} seconds.", file=sys.stderr)
 
-    tokenizer = HFTokenizer(tokenizer_path) if tokenizer_path.suffix == ".json" else Tokenizer(tokenizer_path)
-    encoded = tokenizer.encode(prompt, bos=True, eos=False, device=device)
+    if prompt_ids is not None:
+        tokenizer = None
+        encoded = torch.tensor([int(t) for t in prompt_ids.split(",")], dtype=torch.int64, device=device)
+    else:
+        tokenizer = HFTokenizer(tokenizer_path) if tokenizer_path.suffix == ".json" else Tokenizer(tokenizer_path)
+        encoded = tokenizer.encode(prompt, bos=True, eos=False, device=device)
     prompt_length = encoded.size(0)
 
     torch.manual_seed(1234)
@@ -152,7 +165,7 @@ def main(
         torch.cuda.synchronize()
         t = time.perf_counter() - t0
         model.reset_cache()
-        print(tokenizer.decode(y))
+        print(tokenizer.decode(y) if tokenizer is not None else ",".join(str(int(t)) for t in y))
         n_new = y.size(0) - prompt_length
         print(f"Time for inference {i + 1}: {t:.02f} sec total, {n_new / t:.02f} tokens/sec", file=sys.stderr)
     print(f"Memory used: {torch.cuda.max_memory_reserved() / 1e9:.02f} GB", file=sys.stderr)
@@ -170,7 +183,9 @@ if __name__ == "__main__":
     ap.add_argument("--checkpoint_path", type=Path, default=Path("checkpoints/lit-llama/7B/lit-llama.pth"))
     ap.add_argument("--tokenizer_path", type=Path, default=Path("checkpoints/lit-llama/tokenizer.model"))
     ap.add_argument("--quantize", default=None, choices=[None, "llm.int8", "gptq.int4", "gptq.int8"])
+    ap.add_argument("--prompt_ids", default=None, help="comma-separated token ids instead of --prompt (no tokenizer needed)")
+    ap.add_argument("--dtype", default=None, choices=[None, "bfloat16", "float32"])
     a = ap.parse_args()
     main(a.prompt, num_samples=a.num_samples, max_new_tokens=a.max_new_tokens, top_k=a.top_k,
          temperature=a.temperature, checkpoint_path=a.checkpoint_path, tokenizer_path=a.tokenizer_path,
-         quantize=a.quantize)
+         quantize=a.quantize, prompt_ids=a.prompt_ids, dtype=a.dtype)

@@ -53,6 +53,11 @@ class LepalornConfig:
     def n_layer(self) -> int:
         return len(self.layers)
 
+    @property
+    def block_size(self) -> int:
+        """No learned or tabulated position limit: rotary angles are computed for whatever length the cache is given."""
+        return 1 << 30
+
     @classmethod
     def from_dict(cls, cfg: dict, shapes: Optional[Dict[str, Tuple[int, ...]]] = None) -> "LepalornConfig":
         """From the dictionary of a ``config.json``; sizes it leaves out are taken from the tensors' shapes."""
@@ -142,6 +147,7 @@ class LepalornBlock(nn.Module):
 
 class Lepalorn(nn.Module):
     architecture = ARCHITECTURE
+    use_fused_decode = False       # generate(): the per-op sampling loop drives this model
     use_step_graph = True          # single-token steps replay one CUDA graph per (batch, ring length)
     prefill_portion = 4096         # most tokens one pass appends; longer prompts run as several passes
     layer_probe = None             # callable(layer index, fp32 stream [B*T, width]) after every layer, for inspection

@@ -88,9 +88,7 @@ def save_safetensors(tensors: Dict[str, torch.Tensor], path) -> None:
     header, blobs, at = {}, [], 0
     for name, t in tensors.items():
         t = t.detach().cpu().contiguous()
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
-        if t.dim() == 0:
-            raw = t.reshape(1).view(torch.uint8).numpy().tobytes()
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [at, at + len(raw)]}
         blobs.append(raw)
         at += len(raw)

@@ -39,15 +39,16 @@ def test_gain_norm_add_and_depth_mix(dtype):
     out = t_stack[n - 1]
     nxt = torch.empty((rows, dim), device="cuda")
     act = torch.empty((rows, dim), device="cuda", dtype=dtype)
-    gain_norm_add_mix(dev(x), dev(y, dtype), dev([gain]), eps, out=out, stack=t_stack, mix_w=dev(w), n_mix=n, nxt=nxt, nxt_act=act)
+    tx, ty, tg, tw = dev(x), dev(y, dtype), dev([gain]), dev(w)
+    gain_norm_add_mix(tx, ty, tg, eps, out=out, stack=t_stack, mix_w=tw, n_mix=n, nxt=nxt, nxt_act=act)
     close(host(out), res, 1e-5)
     mixed = w[n - 1] * res + sum(w[j] * stack[j] for j in range(n - 1))
     close(host(nxt), mixed, 1e-5)
     close(host(act), mixed, TOL[dtype])
     # without a mix, and the norm alone on an fp32 stream
-    gain_norm_add_mix(dev(x), dev(y, dtype), dev([gain]), eps, out=nxt, nxt_act=act)
+    gain_norm_add_mix(tx, ty, tg, eps, out=nxt, nxt_act=act)
     close(host(nxt), res, 1e-5)
-    gain_norm_add_mix(None, dev(x), dev([gain]), eps, nxt_act=act)
+    gain_norm_add_mix(None, tx, tg, eps, nxt_act=act)
     close(host(act), gain * O.rms(x, eps), TOL[dtype])
 
 
@@ -73,8 +74,9 @@ def _append(dtype, d, norm_w, pos, S, KR, R, dims, base, eps, cache=None, B=1):
         cache = torch.zeros((B, S, KR + R), device="cuda", dtype=dtype)
     proj = torch.zeros((B * T, 3 + KR + R), device="cuda", dtype=dtype)    # the rows sit at column 3 of a wider projection
     proj[:, 3:] = dev(d, dtype)
-    N.call("ll_latent_kv_append", N.ptr(proj), N.dtype_code(dtype), proj.shape[1], 3, N.ptr(dev(norm_w)), eps, N.ptr(rope),
-           N.ptr(torch.tensor(pos, dtype=torch.int32, device="cuda")), N.ptr(cache), B, T, KR, R, dims, S, N.stream())
+    w, p = dev(norm_w), torch.tensor(pos, dtype=torch.int32, device="cuda")     # named: alive until the launch
+    N.call("ll_latent_kv_append", N.ptr(proj), N.dtype_code(dtype), proj.shape[1], 3, N.ptr(w), eps, N.ptr(rope),
+           N.ptr(p), N.ptr(cache), B, T, KR, R, dims, S, N.stream())
     return cache, rope
 
 
@@ -114,8 +116,9 @@ def _attend(dtype, q_lat, q_rot, gate, cache_rows, pos, S, window, scale, dims, 
     ql = dev(q_lat.transpose(1, 0, 2), dtype).contiguous()                 # [H, T, KR]
     out = torch.empty_like(ql)
     scratch = torch.empty(max(1, N.call_ret("ll_latent_attn_scratch_bytes", T, H, KR, splits) // 4), device="cuda")
+    p = torch.tensor(pos, dtype=torch.int32, device="cuda")
     N.call("ll_latent_attn", N.ptr(ql), T * KR, KR, N.ptr(proj), stride, 3, 3 + R, H * (3 + R), N.ptr(rope),
-           N.ptr(torch.tensor(pos, dtype=torch.int32, device="cuda")), N.ptr(ring), N.ptr(out), T * KR, KR, N.dtype_code(dtype), 1, T,
+           N.ptr(p), N.ptr(ring), N.ptr(out), T * KR, KR, N.dtype_code(dtype), 1, T,
            H, KR, R, dims, S, window, scale, splits, N.ptr(scratch), N.stream())
     return host(out).transpose(1, 0, 2)                                     # [T, H, KR]
 
@@ -142,7 +145,7 @@ def test_window_edges_with_a_key_that_dominates(dtype, splits):
     return (almost exactly) its row and the query at 137 must not see it; likewise in the first tokens of a sequence."""
     r = np.random.RandomState(3)
     H, KR, R, dims, base, window, scale = 3, 24, 6, 6, 100.0, 37, 0.5
-    S = 64                                                     # the ring has wrapped more than twice by position 137
+    S = 80                                                     # the ring has wrapped by position 137: slot of p is p % 80
     rows = {j: O.bf16_round(0.3 * r.randn(KR + R)).astype(np.float64) for j in range(138 - S, 138)}
     probe = np.zeros(KR)
     probe[5] = 1.0
@@ -172,8 +175,8 @@ def test_a_far_key_among_hundreds_and_the_first_tokens(dtype):
     q_lat = O.bf16_round(0.2 * r.randn(len(pos), H, KR)).astype(np.float64)
     q_rot = np.zeros((len(pos), H, R))
     gate = np.full((len(pos), H), 30.0)                        # gate ~ 1
-    # the query at 649 carries, before rotation, the vector that after rotation by its own angle points along key 60's
-    ang = (649 - 60) * 1.0                                     # frequency of pair 0 is 1
+    # the query at 649 carries, before rotation, the vector that its own rotation turns onto the stored (rotated) key of 60
+    ang = 649 * 1.0                                            # frequency of pair 0 is 1
     q_rot[5, :, 0], q_rot[5, :, 1] = 16 * np.cos(-ang), 16 * np.sin(-ang)
     for splits in (1, 4):
         got = _attend(dtype, q_lat, q_rot, gate, rows, pos, S, window, scale, dims, base, splits, H, KR, R)

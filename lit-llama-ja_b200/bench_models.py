@@ -1,0 +1,220 @@
+"""Throughput of a model family beside LLaMA at equal size (``bench.py --family lepalorn``): prefill tokens/s, batch-1 decode
+tokens/s, and the hot kernels of each timed alone against the measured roofline.  Random weights, layer shapes of real
+models, a few layers each (every layer costs the same).  Timing: CUDA events, warm-up, an L2 flush (a 256 MB write)
+between timed iterations."""
+from __future__ import annotations
+
+import json
+import math
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+# width, layers, heads, nope, rot, v, kv_rank, window, experts, top, ff, shared_ff  (top * ff + shared_ff = LLaMA's n_hidden)
+SIZES = {
+    "w1024": dict(width=1024, layers=4, heads=8, nope=64, rot=32, v=64, kv_rank=256, window=512, experts=16, top=2, ff=768, shared=1280),
+    "w2048": dict(width=2048, layers=4, heads=16, nope=128, rot=64, v=128, kv_rank=512, window=1024, experts=32, top=4, ff=1024, shared=1536),
+    "w4096": dict(width=4096, layers=2, heads=32, nope=128, rot=64, v=128, kv_rank=512, window=2048, experts=32, top=4, ff=2048, shared=2816),
+}
+VOCAB = 32000
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "measured"
+    return 6.65e12, 1.59e15, "fallback"
+
+
+class Timer:
+    def __init__(self, device):
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def __call__(self, fn, iters=5, warmup=3):
+        for _ in range(warmup):
+            fn()
+        ts = []
+        for _ in range(iters):
+            self.flush.fill_(1)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e-3)
+        ts.sort()
+        return ts[len(ts) // 2]
+
+
+def lepalorn_model(s, device, dtype=torch.bfloat16):
+    from lit_llama.latent_attention import LatentAttentionSpec
+    from lit_llama.lepalorn import Lepalorn, LepalornConfig, LepalornLayer
+    from lit_llama.moe import MoESpec
+
+    layers = []
+    for i in range(s["layers"]):
+        mx = LatentAttentionSpec(width=s["width"], heads=s["heads"], nope_dim=s["nope"], rot_dim=s["rot"], v_dim=s["v"],
+                                 kv_rank=s["kv_rank"], window=s["window"], scale=(s["nope"] + s["rot"]) ** -0.5,
+                                 kv_from=(i - 1) if i % 2 == 1 else None)
+        layers.append(LepalornLayer(mx, MoESpec(s["width"], s["experts"], s["top"], s["ff"], 7.0, s["shared"], 7.0)))
+    m = Lepalorn(LepalornConfig(VOCAB, s["width"], 1e-5, 1.0, layers), dtype=dtype, device=device)
+    g = torch.Generator(device=device).manual_seed(0)
+    for n, p in m.named_parameters():
+        if p.dim() >= 2:
+            p.copy_((torch.randn(p.shape, generator=g, device=device) / math.sqrt(p.shape[-1])).to(p.dtype))
+        elif n.endswith("dwa"):
+            p.zero_()
+            p[-1] = 1.0
+    return m.eval()
+
+
+def llama_model(s, device):
+    from lit_llama.model import LLaMA, LLaMAConfig
+
+    cfg = LLaMAConfig(block_size=8192, vocab_size=VOCAB, n_layer=s["layers"], n_head=s["heads"], n_embd=s["width"])
+    with torch.device(device):
+        m = LLaMA(cfg).to(torch.bfloat16)
+    m.apply(m._init_weights)
+    m.use_fused_decode = False          # unquantized: the per-module path, single-token steps as one graph replay
+    m.graph_every_batch = True
+    return m.eval()
+
+
+def end_to_end(model, timer, prompt_len, device, max_seq):
+    idx = torch.randint(0, VOCAB, (1, prompt_len), device=device)
+    pos = torch.arange(prompt_len, device=device)
+
+    def prefill():
+        model.reset_cache()
+        model(idx, max_seq, pos)
+
+    t_prefill = timer(prefill, iters=3, warmup=2)
+    one, p1 = idx[:, :1].contiguous(), torch.arange(prompt_len, prompt_len + 1, device=device)
+    n = 16
+
+    def decode():
+        for _ in range(n):
+            model(one, max_seq, p1)
+
+    t_decode = timer(decode, iters=3, warmup=2) / n
+    return prompt_len / t_prefill, 1.0 / t_decode
+
+
+def kernel_table(s, lep, device, timer, prompt_len):
+    """The hot kernels of one layer alone.  Roofline time = max(flops / tensor peak, bytes / copy bandwidth)."""
+    from torch.nn import functional as F
+
+    from lit_llama import _native as N
+
+    hbm, tflops, which = peaks()
+    bf = torch.bfloat16
+    E, H, KR, R, W = s["width"], s["heads"], s["kv_rank"], s["rot"], s["window"]
+    rows = []
+
+    def add(name, t, flops, nbytes):
+        roof = max(flops / tflops, nbytes / hbm)
+        rows.append(dict(kernel=name, us=round(t * 1e6, 1), roofline_us=round(roof * 1e6, 2), fraction=round(roof / t, 4)))
+
+    blk = lep.blocks[0]
+    for T, tag in ((prompt_len, "prefill"), (1, "decode")):
+        x = torch.randn((T, E), device=device, dtype=bf)
+        pos0 = 0 if T > 1 else prompt_len
+        pos_ids = torch.arange(pos0, pos0 + T, dtype=torch.int32, device=device)
+        lep.reset_cache()
+        lep._ensure_cache(1, prompt_len + 64)
+        lep._ensure_rope(prompt_len + 64)
+        cache = lep.kv_caches[0]
+        cache.normal_()
+        rope = lep._rope[(blk.mix.spec.rot_base, blk.mix.spec.rot_dims)]
+        proj = F.linear(x, blk.mix.w_in)
+        q_lat = torch.randn((H, T, KR), device=device, dtype=bf)
+        o_lat = torch.empty_like(q_lat)
+        splits = 1 if T > 1 else max(1, min(16, (W + 127) // 128))
+        scratch = torch.empty(max(1, N.call_ret("ll_latent_attn_scratch_bytes", T, H, KR, splits) // 4), device=device)
+
+        def attn():
+            N.call("ll_latent_attn", N.ptr(q_lat), T * KR, KR, N.ptr(proj), proj.shape[1], s["nope"], s["nope"] + R, blk.mix.gate_col0,
+                   N.ptr(rope), N.ptr(pos_ids), N.ptr(cache), N.ptr(o_lat), T * KR, KR, N.LL_BF16, 1, T, H, KR, R, R, cache.shape[1], W,
+                   0.1, splits, N.ptr(scratch), N.stream())
+
+        keys = sum(min(W, p + 1) for p in range(pos0, pos0 + T))
+        add(f"latent_attn {tag}", timer(attn), 2.0 * keys * H * (2 * KR + R), 2.0 * (min(W + T, pos0 + T) * (KR + R) + 2 * H * T * KR))
+        # LLaMA's attention at equal heads and head size = nope + rot
+        hs = s["width"] // H
+        q = torch.randn((1, H, T, hs), device=device, dtype=bf)
+        if T > 1:
+            k, v = torch.randn_like(q), torch.randn_like(q)
+            add("llama sdpa prefill (library, full causal)", timer(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True)),
+                2.0 * (T * (T + 1) / 2) * H * 2 * hs, 2.0 * 4 * T * H * hs)
+        elif hs in (32, 64, 128):
+            S = prompt_len + 64
+            kc, vc = torch.randn((1, H, S, hs), device=device, dtype=bf), torch.randn((1, H, S, hs), device=device, dtype=bf)
+            y = torch.empty((1, 1, H * hs), device=device, dtype=bf)
+            p3 = torch.tensor([prompt_len, prompt_len, prompt_len + 1], dtype=torch.int32, device=device)
+            sp = max(1, min(8, (2 * N._fn["ll_sm_count"]()) // H, (S + 63) // 64))
+            ws = N.Workspace.get(device).ensure(attn_bytes=N.attn_scratch_bytes(1, H, hs, sp), attn_counters=H)
+            add("llama decode_attn", timer(lambda: N.call("ll_decode_attn", N.ptr(q), N.ptr(kc), N.ptr(vc), N.ptr(p3), N.ptr(y), N.LL_BF16, 1,
+                                                          H, hs, S, sp, N.ptr(ws.attn_scratch), N.ptr(ws.attn_counters), 0, N.stream())),
+                4.0 * (prompt_len + 1) * H * hs, 2.0 * 2 * (prompt_len + 1) * H * hs)
+        # experts: both grouped GEMMs of the layer / LLaMA's three MLP GEMMs
+        moe = blk.mlp
+        _, w, offsets, perm = moe.route(x)
+        n = T * s["top"]
+        h = torch.empty((n, s["ff"]), dtype=bf, device=device)
+        yy = torch.empty((n, E), dtype=bf, device=device)
+
+        def experts():
+            N.call("ll_moe_grouped_gemm", N.ptr(x), E, N.ptr(moe.w_gu), N.ptr(offsets), N.ptr(perm), 1, N.LL_BF16, n, s["top"], s["experts"],
+                   s["ff"], E, 7.0, 1.702, N.ptr(h), s["ff"], N.stream())
+            N.call("ll_moe_grouped_gemm", N.ptr(h), s["ff"], N.ptr(moe.w_down), N.ptr(offsets), N.ptr(perm), 0, N.LL_BF16, n, s["top"],
+                   s["experts"], E, s["ff"], 0.0, 0.0, N.ptr(yy), E, N.stream())
+
+        used = min(s["experts"], n)
+        add(f"moe grouped GEMMs {tag}", timer(experts), 2.0 * n * 3 * s["ff"] * E, 2.0 * used * 3 * s["ff"] * E)
+        nh = s["top"] * s["ff"] + s["shared"]
+        w1, w2 = torch.randn((2 * nh, E), device=device, dtype=bf), torch.randn((E, nh), device=device, dtype=bf)
+        hh = torch.empty((T, nh), device=device, dtype=bf)
+
+        def mlp():
+            F.linear(x, w1)
+            F.linear(hh, w2)
+
+        add(f"llama MLP GEMMs {tag} (library)", timer(mlp), 2.0 * T * 3 * nh * E, 2.0 * 3 * nh * E)
+    return rows, which
+
+
+def run(args):
+    import sys
+
+    sys.path.insert(0, str(ROOT))
+    from __graft_entry__ import build
+
+    build()
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    timer = Timer(device)
+    prompt_len = 2048
+    out = {"family": "lepalorn", "dtype": "bf16", "data": "synthetic (random weights)", "prompt_len": prompt_len, "batch": 1,
+           "l2": "256 MB written between timed iterations", "sizes": {}}
+    names = [n for n in SIZES if not getattr(args, "size", None) or n == args.size]
+    for name in names:
+        s = SIZES[name]
+        with torch.no_grad():
+            lep = lepalorn_model(s, device)
+            pre, dec = end_to_end(lep, timer, prompt_len, device, prompt_len + 64)
+            rows, which = kernel_table(s, lep, device, timer, prompt_len)
+            del lep
+            torch.cuda.empty_cache()
+            ll = llama_model(s, device)
+            lpre, ldec = end_to_end(ll, timer, prompt_len, device, prompt_len + 64)
+            del ll
+            torch.cuda.empty_cache()
+        out["sizes"][name] = {"config": s, "lepalorn": {"prefill_tokens_per_s": round(pre), "decode_tokens_per_s": round(dec, 1)},
+                              "llama_bf16_same_width": {"prefill_tokens_per_s": round(lpre), "decode_tokens_per_s": round(ldec, 1)},
+                              "kernels": rows, "roofline": f"of {which}"}
+    print(json.dumps(out))
+    return 0

@@ -206,6 +206,249 @@ __global__ void __launch_bounds__(LA_THREADS) latent_attn_kernel(const LatentAtt
   }
 }
 
+// ---- bf16 tensor-core form (mma.sync m16n8k16, fp32 scores / softmax / accumulation) ----
+// A block owns 32 query rows = (a few consecutive tokens) x (up to 32 heads) and walks the union of their windows in
+// chunks of 64 cache rows: S = Q K^T (all heads against the same rows), online softmax in fp32, O += P C with the
+// accumulators of the 32 x kv_rank output split by columns over the 8 warps (NTW n-tiles of 8 columns each).
+constexpr int LM_ROWS = 32, LM_KC = 64, LM_THREADS = 256;
+
+__device__ __forceinline__ void la_cp_async16(void* smem, const void* gmem, bool valid) {
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem)), "l"(gmem), "r"(n) : "memory");
+}
+__device__ __forceinline__ void la_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void la_ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void la_ldmatrix_x2_trans(uint32_t (&r)[2], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_u32(p)));
+}
+
+struct LatentMmaGeom {
+  int HB, TQ, DKP, pitch;   // heads and tokens per block (HB * TQ <= 32), padded row length, shared-memory row pitch (elements)
+};
+
+template <int NTW>
+__global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const LatentAttnParams P, const LatentMmaGeom G) {
+  extern __shared__ __align__(16) unsigned char la_smem[];
+  const int KR = P.kv_rank, R = P.rot_dim, Dk = KR + R;
+  const int pitch = G.pitch;
+  __nv_bfloat16* Qs = (__nv_bfloat16*)la_smem;                 // [32][pitch]
+  __nv_bfloat16* Ks = Qs + LM_ROWS * pitch;                    // [64][pitch]
+  __nv_bfloat16* Ps = Ks + LM_KC * pitch;                      // [32][64 + 8]
+  float* Ss = (float*)(Ps + LM_ROWS * (LM_KC + 8));            // [32][64 + 1]
+  float* m_run = Ss + LM_ROWS * (LM_KC + 1);                   // [32]
+  float* l_run = m_run + LM_ROWS;
+  float* corr = l_run + LM_ROWS;
+  int* row_pos = (int*)(corr + LM_ROWS);                       // [32] position of the row's token, -1: padding row
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tiles_t = (P.Tn + G.TQ - 1) / G.TQ;
+  const int b = blockIdx.x / tiles_t, t0 = (blockIdx.x - b * tiles_t) * G.TQ;
+  const int ntok = min(G.TQ, P.Tn - t0);
+  const int h0 = blockIdx.y * G.HB, HB = min(G.HB, P.H - h0);
+  const int sp = blockIdx.z;
+  const __nv_bfloat16* q_lat = (const __nv_bfloat16*)P.q_lat;
+  const __nv_bfloat16* proj = (const __nv_bfloat16*)P.proj;
+
+  if (tid < LM_ROWS) {
+    const int tq = tid / G.HB, hh = tid - tq * G.HB;
+    row_pos[tid] = (tq < ntok && hh < HB) ? P.pos_ids[t0 + tq] : -1;
+    m_run[tid] = -INFINITY;
+    l_run[tid] = 0.f;
+  }
+  // queries: latent part as it is, rotary part rotated in fp32, zero padding
+  for (int idx = tid; idx < LM_ROWS * G.DKP; idx += LM_THREADS) {
+    const int r = idx / G.DKP, i = idx - r * G.DKP;
+    const int tq = r / G.HB, hh = r - tq * G.HB;
+    float v = 0.f;
+    if (tq < ntok && hh < HB && i < Dk) {
+      const size_t m = (size_t)b * P.Tn + t0 + tq;
+      if (i < KR) {
+        v = __bfloat162float(q_lat[(size_t)((h0 + hh) * P.qs_h + (long long)m * P.qs_m + i)]);
+      } else {
+        const int d = i - KR;
+        const __nv_bfloat16* qr = proj + m * P.proj_stride + P.q_rot_col0 + (size_t)(h0 + hh) * P.q_head_stride;
+        if ((d | 1) < P.rot_dims) {
+          const float* cs = P.rope + (size_t)P.pos_ids[t0 + tq] * P.rot_dims + (d & ~1);
+          const float u = __bfloat162float(qr[d & ~1]), w = __bfloat162float(qr[d | 1]);
+          v = (d & 1) ? (w * cs[0] + u * cs[1]) : (u * cs[0] - w * cs[1]);
+        } else {
+          v = __bfloat162float(qr[d]);
+        }
+      }
+    }
+    Qs[r * pitch + i] = __float2bfloat16_rn(v);
+  }
+  // zero the padding columns of the key rows once (the loads below never touch them)
+  for (int idx = tid; idx < LM_KC * (G.DKP - Dk); idx += LM_THREADS) {
+    const int r = idx / (G.DKP - Dk), i = Dk + idx - r * (G.DKP - Dk);
+    Ks[r * pitch + i] = __float2bfloat16_rn(0.f);
+  }
+
+  const int p_first = P.pos_ids[t0], p_last = P.pos_ids[t0 + ntok - 1];
+  const int lo = (P.window > 0 && p_first - P.window + 1 > 0) ? p_first - P.window + 1 : 0;
+  const int n_all = p_last - lo + 1;
+  const int per = (n_all + P.splits - 1) / P.splits;
+  const int j_begin = lo + sp * per;
+  const int j_end = min(p_last + 1, j_begin + per);
+  const __nv_bfloat16* cache = (const __nv_bfloat16*)P.cache + (size_t)b * P.cache_len * Dk;
+  const bool vec = (Dk % 8 == 0) && (((uintptr_t)cache & 15) == 0);
+
+  float acc[2][NTW][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < NTW; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[i][j][q] = 0.f;
+  const int wcol0 = warp * NTW * 8;            // this warp's first output column
+  __syncthreads();
+
+  for (int j0 = j_begin; j0 < j_end; j0 += LM_KC) {
+    const int nk = min(LM_KC, j_end - j0);
+    if (vec) {
+      const int cpr = Dk / 8;
+      for (int ch = tid; ch < LM_KC * cpr; ch += LM_THREADS) {
+        const int jj = ch / cpr, c8 = (ch - jj * cpr) * 8;
+        const bool ok = jj < nk;
+        la_cp_async16(Ks + jj * pitch + c8, cache + (size_t)((ok ? j0 + jj : j0) % P.cache_len) * Dk + c8, ok);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else {
+      for (int idx = tid; idx < LM_KC * Dk; idx += LM_THREADS) {
+        const int jj = idx / Dk, i = idx - jj * Dk;
+        Ks[jj * pitch + i] = jj < nk ? cache[(size_t)((j0 + jj) % P.cache_len) * Dk + i] : __float2bfloat16_rn(0.f);
+      }
+    }
+    __syncthreads();
+    {   // S = Q K^T: warp -> m-tile (warp & 1), key columns (warp >> 1) * 16 .. + 15
+      const int mt = warp & 1, np = warp >> 1;
+      float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      for (int ks = 0; ks < G.DKP / 16; ++ks) {
+        uint32_t af[4], bf[4];
+        la_ldmatrix_x4(af, Qs + (mt * 16 + (lane & 15)) * pitch + ks * 16 + (lane >> 4) * 8);
+        la_ldmatrix_x4(bf, Ks + (np * 16 + (lane & 7) + (lane >> 4) * 8) * pitch + ks * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16_16816(sacc[0], af[0], af[1], af[2], af[3], bf[0], bf[1]);
+        mma_bf16_16816(sacc[1], af[0], af[1], af[2], af[3], bf[2], bf[3]);
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int r = mt * 16 + (lane >> 2) + (q >> 1) * 8;
+          const int col = np * 16 + j * 8 + (lane & 3) * 2 + (q & 1);
+          const int pr = row_pos[r], jpos = j0 + col;
+          const bool vis = pr >= 0 && col < nk && jpos <= pr && (P.window <= 0 || jpos > pr - P.window);
+          Ss[r * (LM_KC + 1) + col] = vis ? sacc[j][q] * P.scale : -INFINITY;
+        }
+    }
+    __syncthreads();
+    for (int r = warp * 4; r < warp * 4 + 4; ++r) {   // online softmax: 4 rows per warp, 2 columns per lane
+      const float s0 = Ss[r * (LM_KC + 1) + lane], s1 = Ss[r * (LM_KC + 1) + lane + 32];
+      const float mo = m_run[r];
+      const float mn = fmaxf(mo, warp_max(fmaxf(s0, s1)));
+      const float p0 = (s0 == -INFINITY) ? 0.f : expf(s0 - mn), p1 = (s1 == -INFINITY) ? 0.f : expf(s1 - mn);
+      const __nv_bfloat16 b0 = __float2bfloat16_rn(p0), b1 = __float2bfloat16_rn(p1);
+      Ps[r * (LM_KC + 8) + lane] = b0;
+      Ps[r * (LM_KC + 8) + lane + 32] = b1;
+      const float sum = warp_sum(__bfloat162float(b0) + __bfloat162float(b1));   // the weights as the product below sees them
+      if (lane == 0) {
+        const float c = (mo == -INFINITY) ? 0.f : expf(mo - mn);
+        corr[r] = c;
+        l_run[r] = l_run[r] * c + sum;
+        m_run[r] = mn;
+      }
+    }
+    __syncthreads();
+    if (wcol0 < KR) {   // O = O * corr + P C over this warp's columns
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const float c0 = corr[i * 16 + (lane >> 2)], c1 = corr[i * 16 + (lane >> 2) + 8];
+#pragma unroll
+        for (int j = 0; j < NTW; ++j) { acc[i][j][0] *= c0; acc[i][j][1] *= c0; acc[i][j][2] *= c1; acc[i][j][3] *= c1; }
+      }
+#pragma unroll
+      for (int ks = 0; ks < LM_KC / 16; ++ks) {
+        uint32_t af[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) la_ldmatrix_x4(af[i], Ps + (i * 16 + (lane & 15)) * (LM_KC + 8) + ks * 16 + (lane >> 4) * 8);
+        if (NTW == 1) {
+          uint32_t bf[2];
+          la_ldmatrix_x2_trans(bf, Ks + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * pitch + wcol0);
+#pragma unroll
+          for (int i = 0; i < 2; ++i) mma_bf16_16816(acc[i][0], af[i][0], af[i][1], af[i][2], af[i][3], bf[0], bf[1]);
+        } else {
+#pragma unroll
+          for (int jp = 0; jp < NTW / 2; ++jp) {
+            if (wcol0 + jp * 16 >= KR) break;
+            uint32_t bf[4];
+            la_ldmatrix_x4_trans(bf, Ks + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * pitch + wcol0 + jp * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              mma_bf16_16816(acc[i][2 * jp], af[i][0], af[i][1], af[i][2], af[i][3], bf[0], bf[1]);
+              mma_bf16_16816(acc[i][2 * jp + 1], af[i][0], af[i][1], af[i][2], af[i][3], bf[2], bf[3]);
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  __nv_bfloat16* out = (__nv_bfloat16*)P.out;
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < NTW; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int r = i * 16 + (lane >> 2) + (q >> 1) * 8;
+        const int col = wcol0 + j * 8 + (lane & 3) * 2 + (q & 1);
+        if (row_pos[r] < 0 || col >= KR) continue;
+        const int tq = r / G.HB, hh = r - tq * G.HB;
+        const size_t m = (size_t)b * P.Tn + t0 + tq;
+        if (P.splits == 1) {
+          float g = 1.f;
+          if (P.gate_col0 >= 0) g = 1.f / (1.f + expf(-__bfloat162float(proj[m * P.proj_stride + P.gate_col0 + h0 + hh])));
+          out[(size_t)((h0 + hh) * P.os_h + (long long)m * P.os_m + col)] = __float2bfloat16_rn(acc[i][j][q] / l_run[r] * g);
+        } else {
+          P.scratch[((m * P.H + h0 + hh) * P.splits + sp) * (KR + 2) + col] = acc[i][j][q];
+        }
+      }
+  if (P.splits > 1 && tid < LM_ROWS && row_pos[tid] >= 0) {
+    const int tq = tid / G.HB, hh = tid - tq * G.HB;
+    const size_t m = (size_t)b * P.Tn + t0 + tq;
+    float* rec = P.scratch + ((m * P.H + h0 + hh) * P.splits + sp) * (KR + 2) + KR;
+    rec[0] = m_run[tid];
+    rec[1] = l_run[tid];
+  }
+}
+
+static size_t latent_mma_smem(int pitch) {
+  return sizeof(__nv_bfloat16) * ((size_t)(LM_ROWS + LM_KC) * pitch + (size_t)LM_ROWS * (LM_KC + 8)) +
+         sizeof(float) * ((size_t)LM_ROWS * (LM_KC + 1) + 3 * LM_ROWS) + sizeof(int) * LM_ROWS;
+}
+
+template <int NTW>
+static int launch_latent_mma(const LatentAttnParams& P, const LatentMmaGeom& G, int B, cudaStream_t st) {
+  const size_t smem = latent_mma_smem(G.pitch);
+  static size_t configured = 0;
+  if (smem > configured) {
+    LL_CUDA(cudaFuncSetAttribute(latent_attn_mma_kernel<NTW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  dim3 grid(B * ((P.Tn + G.TQ - 1) / G.TQ), (P.H + G.HB - 1) / G.HB, P.splits);
+  latent_attn_mma_kernel<NTW><<<grid, LM_THREADS, smem, st>>>(P, G);
+  LL_LAUNCH_OK("latent_attn_mma_kernel");
+  return LL_OK;
+}
+
 // Merge the splits of one (token, head) in split order: out = sum_s e^(m_s - m) acc_s / sum_s e^(m_s - m) l_s, times the gate.
 template <typename T>
 __global__ void latent_attn_combine_kernel(const LatentAttnParams P) {
@@ -306,8 +549,28 @@ int ll_latent_attn(const void* q_lat, long long qs_h, long long qs_m, const void
     return LL_ERR_UNSUPPORTED;
   }
   cudaStream_t st = (cudaStream_t)stream;
+  bool done = false;
+  if (dtype == LL_BF16 && kv_rank <= 512) {   // tensor-core kernel; the fp32 path and very long rows take the kernel below
+    LatentMmaGeom G;
+    G.HB = n_head < LM_ROWS ? n_head : LM_ROWS;
+    G.TQ = LM_ROWS / G.HB < T ? LM_ROWS / G.HB : T;
+    if (G.TQ < 1) G.TQ = 1;
+    G.DKP = (Dk + 15) / 16 * 16;
+    G.pitch = G.DKP + 8;
+    if (latent_mma_smem(G.pitch) <= 200 * 1024) {
+      const int cols_per_warp = (kv_rank + 7) / 8;
+      int rc;
+      if (cols_per_warp <= 8) rc = launch_latent_mma<1>(P, G, B, st);
+      else if (cols_per_warp <= 16) rc = launch_latent_mma<2>(P, G, B, st);
+      else if (cols_per_warp <= 32) rc = launch_latent_mma<4>(P, G, B, st);
+      else rc = launch_latent_mma<8>(P, G, B, st);
+      if (rc != LL_OK) return rc;
+      done = true;
+    }
+  }
   dim3 grid(B * T, (n_head + P.HG - 1) / P.HG, splits);
-  if (dtype == LL_F32) {
+  if (done) {
+  } else if (dtype == LL_F32) {
     LL_CUDA(cudaFuncSetAttribute(latent_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     latent_attn_kernel<float><<<grid, LA_THREADS, smem, st>>>(P);
   } else if (dtype == LL_BF16) {
@@ -317,7 +580,7 @@ int ll_latent_attn(const void* q_lat, long long qs_h, long long qs_m, const void
     set_error("latent_attn: unsupported dtype %d", dtype);
     return LL_ERR_UNSUPPORTED;
   }
-  LL_LAUNCH_OK("latent_attn_kernel");
+  if (!done) LL_LAUNCH_OK("latent_attn_kernel");
   if (splits > 1) {
     dim3 g2(B * T, n_head);
     if (dtype == LL_F32) latent_attn_combine_kernel<float><<<g2, 128, 0, st>>>(P);

@@ -199,6 +199,155 @@ __global__ void __launch_bounds__(GG_THREADS) moe_grouped_gemm_kernel(const T* _
   }
 }
 
+// ---- bf16 tensor-core form of the same grouped GEMM (mma.sync m16n8k16, fp32 accumulation) ----
+// 128 threads; a block = BM sorted rows of one expert x 64 output columns (x2 matrices for the GLU), K in steps of 64
+// through a two-stage cp.async ring.  Needs 16-byte aligned rows (K, lda multiples of 8); other shapes take the kernel above.
+constexpr int GM_BN = 64, GM_BK = 64, GM_PITCH = GM_BK + 8, GM_THREADS = 128;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem)), "l"(gmem), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N_>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N_) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+
+template <int BM, int MODE>
+__global__ void __launch_bounds__(GM_THREADS) moe_grouped_gemm_mma_kernel(
+    const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, const int32_t* __restrict__ offsets,
+    const int32_t* __restrict__ perm, int top, int X, int N, int K, float limit, float alpha, __nv_bfloat16* __restrict__ c, int ldc) {
+  constexpr int NB = MODE == MODE_GLU ? 2 : 1;
+  constexpr int WARPS_M = BM >= 32 ? 2 : 1, WARPS_N = 4 / WARPS_M;
+  constexpr int WM = BM / WARPS_M, WN = GM_BN / WARPS_N, MT = WM / 16, NT = WN / 8;
+  extern __shared__ __align__(16) unsigned char gm_smem[];
+  __nv_bfloat16* As = (__nv_bfloat16*)gm_smem;                               // [2][BM][PITCH]
+  __nv_bfloat16* Bs = As + 2 * BM * GM_PITCH;                                // [2][NB][BN][PITCH]
+  __shared__ int32_t src_row[BM], dst_row[BM];
+  __shared__ int s_e, s_r0, s_cnt;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) {
+    int t = blockIdx.x, e = 0, found = -1;
+    for (; e < X; ++e) {
+      const int cnt = offsets[e + 1] - offsets[e];
+      const int tiles = (cnt + BM - 1) / BM;
+      if (t < tiles) { found = e; break; }
+      t -= tiles;
+    }
+    s_e = found;
+    if (found >= 0) {
+      s_r0 = offsets[found] + t * BM;
+      s_cnt = min(BM, offsets[found + 1] - s_r0);
+    }
+  }
+  __syncthreads();
+  if (s_e < 0) return;
+  const int e = s_e, r0 = s_r0, cnt = s_cnt;
+  const int n0 = blockIdx.y * GM_BN;
+  for (int i = tid; i < BM; i += GM_THREADS) {
+    const int r = r0 + min(i, cnt - 1);
+    const int pr = perm[r];
+    src_row[i] = MODE == MODE_GLU ? pr / top : r;
+    dst_row[i] = MODE == MODE_GLU ? r : pr;
+  }
+  __syncthreads();
+  const __nv_bfloat16* we = w + (size_t)e * NB * N * K;
+
+  auto load_stage = [&](int stage, int k0) {
+    __nv_bfloat16* as = As + stage * BM * GM_PITCH;
+    for (int ch = tid; ch < BM * (GM_BK / 8); ch += GM_THREADS) {
+      const int r = ch / (GM_BK / 8), kc = (ch % (GM_BK / 8)) * 8;
+      const bool ok = r < cnt && k0 + kc < K;
+      cp_async16(as + r * GM_PITCH + kc, a + (size_t)src_row[r] * lda + (ok ? k0 + kc : 0), ok);
+    }
+    __nv_bfloat16* bs = Bs + stage * NB * GM_BN * GM_PITCH;
+    for (int ch = tid; ch < NB * GM_BN * (GM_BK / 8); ch += GM_THREADS) {
+      const int b = ch / (GM_BN * (GM_BK / 8)), rem = ch % (GM_BN * (GM_BK / 8));
+      const int n = rem / (GM_BK / 8), kc = (rem % (GM_BK / 8)) * 8;
+      const bool ok = n0 + n < N && k0 + kc < K;
+      cp_async16(bs + (b * GM_BN + n) * GM_PITCH + kc, we + ((size_t)b * N + (ok ? n0 + n : 0)) * K + (ok ? k0 + kc : 0), ok);
+    }
+    cp_async_commit();
+  };
+
+  float acc[NB][MT][NT][4];
+#pragma unroll
+  for (int b = 0; b < NB; ++b)
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[b][i][j][q] = 0.f;
+  const int wm0 = (warp / WARPS_N) * WM, wn0 = (warp % WARPS_N) * WN;
+  const int nk = (K + GM_BK - 1) / GM_BK;
+  load_stage(0, 0);
+  for (int kt = 0; kt < nk; ++kt) {
+    if (kt + 1 < nk) { load_stage((kt + 1) & 1, (kt + 1) * GM_BK); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    __syncthreads();
+    const __nv_bfloat16* as = As + (kt & 1) * BM * GM_PITCH;
+    const __nv_bfloat16* bs = Bs + (kt & 1) * NB * GM_BN * GM_PITCH;
+#pragma unroll
+    for (int ks = 0; ks < GM_BK / 16; ++ks) {
+      uint32_t af[MT][4];
+#pragma unroll
+      for (int i = 0; i < MT; ++i) ldmatrix_x4(af[i], as + (wm0 + i * 16 + (lane & 15)) * GM_PITCH + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int b = 0; b < NB; ++b)
+#pragma unroll
+        for (int jp = 0; jp < NT / 2; ++jp) {
+          uint32_t bf[4];
+          ldmatrix_x4(bf, bs + (b * GM_BN + wn0 + jp * 16 + (lane & 7) + (lane >> 4) * 8) * GM_PITCH + ks * 16 + ((lane >> 3) & 1) * 8);
+#pragma unroll
+          for (int i = 0; i < MT; ++i) {
+            mma_bf16_16816(acc[b][i][2 * jp], af[i][0], af[i][1], af[i][2], af[i][3], bf[0], bf[1]);
+            mma_bf16_16816(acc[b][i][2 * jp + 1], af[i][0], af[i][1], af[i][2], af[i][3], bf[2], bf[3]);
+          }
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int r = wm0 + i * 16 + (lane >> 2) + (q >> 1) * 8;
+        const int col = n0 + wn0 + j * 8 + (lane & 3) * 2 + (q & 1);
+        if (r >= cnt || col >= N) continue;
+        float v;
+        if (MODE == MODE_GLU) {
+          const float g = fminf(acc[0][i][j][q], limit);
+          const float u = fminf(fmaxf(acc[NB - 1][i][j][q], -limit), limit);
+          v = g / (1.f + expf(-alpha * g)) * (u + 1.f);
+        } else {
+          v = acc[0][i][j][q];
+        }
+        c[(size_t)dst_row[r] * ldc + col] = __float2bfloat16_rn(v);
+      }
+}
+
+template <int BM, int MODE>
+static int launch_grouped_mma(const void* a, int lda, const void* w, const int32_t* offsets, const int32_t* perm, int top, int X, int N,
+                              int K, float limit, float alpha, void* c, int ldc, int n_rows, cudaStream_t st) {
+  constexpr int NB = MODE == MODE_GLU ? 2 : 1;
+  const size_t smem = sizeof(__nv_bfloat16) * 2 * (BM + NB * GM_BN) * GM_PITCH;
+  static bool once = false;
+  if (!once) {
+    LL_CUDA(cudaFuncSetAttribute(moe_grouped_gemm_mma_kernel<BM, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    once = true;
+  }
+  dim3 grid((n_rows + BM - 1) / BM + X, (N + GM_BN - 1) / GM_BN);
+  moe_grouped_gemm_mma_kernel<BM, MODE><<<grid, GM_THREADS, smem, st>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, offsets, perm,
+                                                                       top, X, N, K, limit, alpha, (__nv_bfloat16*)c, ldc);
+  LL_LAUNCH_OK("moe_grouped_gemm_mma_kernel");
+  return LL_OK;
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const float* __restrict__ expert_w, int top,
                                    const T* __restrict__ shared_y, int shared_ld, const T* __restrict__ shared_gate,
@@ -280,6 +429,13 @@ int ll_moe_grouped_gemm(const void* a, int lda, const void* w, const int32_t* of
                     : (small ? launch_grouped<T, 1, MODE_DOWN>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st) \
                              : launch_grouped<T, 4, MODE_DOWN>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st)))
   if (dtype == LL_F32) return LL_GG(float);
+  if (dtype == LL_BF16 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0) {
+    if (mode == MODE_GLU)
+      return small ? launch_grouped_mma<16, MODE_GLU>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st)
+                   : launch_grouped_mma<64, MODE_GLU>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st);
+    return small ? launch_grouped_mma<16, MODE_DOWN>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st)
+                 : launch_grouped_mma<64, MODE_DOWN>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st);
+  }
   if (dtype == LL_BF16) return LL_GG(__nv_bfloat16);
 #undef LL_GG
   set_error("moe_grouped_gemm: unsupported dtype %d", dtype);

@@ -188,12 +188,12 @@ def test_a_far_key_among_hundreds_and_the_first_tokens(dtype):
 
 
 @pytest.mark.parametrize("dtype", DT)
-@pytest.mark.parametrize("shape", [(11, 40, 7, 3), (64, 33, 1, 1), (5, 24, 4, 4), (300, 96, 16, 2)])
+@pytest.mark.parametrize("shape", [(11, 40, 7, 3, 12), (64, 33, 1, 1, 12), (5, 24, 4, 4, 16), (300, 96, 16, 2, 24), (700, 64, 3, 2, 72)])
 def test_router_permutation_and_grouped_experts(dtype, shape):
     from lit_llama.moe import MoE, MoESpec
 
-    M, width, X, top = shape
-    ff, sff = 12, 9
+    M, width, X, top, ff = shape      # widths / ff that are and are not multiples of 8: tensor-core and plain kernels
+    sff = 9
     r = np.random.RandomState(5)
     cfgf = O.mlp_cfg(X, top, ff, 0.6, sff, 0.9)
     mc = O.model_cfg(8, width, [(O.mixer_cfg(1, 2, 2, 2, 2, 2), cfgf)])

@@ -133,7 +133,7 @@ def kernel_table(s, lep, device, timer, prompt_len):
         proj = F.linear(x, blk.mix.w_in)
         q_lat = torch.randn((H, T, KR), device=device, dtype=bf)
         o_lat = torch.empty_like(q_lat)
-        splits = 1 if T > 1 else max(1, min(16, (W + 127) // 128))
+        splits = 1 if T > 1 else max(1, min(16, (W + 63) // 64))
         scratch = torch.empty(max(1, N.call_ret("ll_latent_attn_scratch_bytes", T, H, KR, splits) // 4), device=device)
 
         def attn():

@@ -238,8 +238,8 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
   const int KR = P.kv_rank, R = P.rot_dim, Dk = KR + R;
   const int pitch = G.pitch;
   __nv_bfloat16* Qs = (__nv_bfloat16*)la_smem;                 // [32][pitch]
-  __nv_bfloat16* Ks = Qs + LM_ROWS * pitch;                    // [64][pitch]
-  __nv_bfloat16* Ps = Ks + LM_KC * pitch;                      // [32][64 + 8]
+  __nv_bfloat16* Ks0 = Qs + LM_ROWS * pitch;                   // [2 stages][64][pitch]
+  __nv_bfloat16* Ps = Ks0 + 2 * LM_KC * pitch;                 // [32][64 + 8]
   float* Ss = (float*)(Ps + LM_ROWS * (LM_KC + 8));            // [32][64 + 1]
   float* m_run = Ss + LM_ROWS * (LM_KC + 1);                   // [32]
   float* l_run = m_run + LM_ROWS;
@@ -261,33 +261,56 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
     m_run[tid] = -INFINITY;
     l_run[tid] = 0.f;
   }
-  // queries: latent part as it is, rotary part rotated in fp32, zero padding
-  for (int idx = tid; idx < LM_ROWS * G.DKP; idx += LM_THREADS) {
-    const int r = idx / G.DKP, i = idx - r * G.DKP;
-    const int tq = r / G.HB, hh = r - tq * G.HB;
-    float v = 0.f;
-    if (tq < ntok && hh < HB && i < Dk) {
-      const size_t m = (size_t)b * P.Tn + t0 + tq;
-      if (i < KR) {
-        v = __bfloat162float(q_lat[(size_t)((h0 + hh) * P.qs_h + (long long)m * P.qs_m + i)]);
-      } else {
-        const int d = i - KR;
+  // queries: latent part as it is (16-byte pieces when rows allow), rotary part rotated in fp32, zero padding
+  const bool qvec = (KR % 8 == 0) && (P.qs_h % 8 == 0) && (P.qs_m % 8 == 0) && (((uintptr_t)q_lat & 15) == 0);
+  if (qvec) {
+    const int cpr = KR / 8;
+    for (int ch = tid; ch < LM_ROWS * cpr; ch += LM_THREADS) {
+      const int r = ch / cpr, c8 = (ch - r * cpr) * 8;
+      const int tq = r / G.HB, hh = r - tq * G.HB;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (tq < ntok && hh < HB) {
+        const size_t m = (size_t)b * P.Tn + t0 + tq;
+        v = *(const uint4*)(q_lat + (size_t)((h0 + hh) * P.qs_h + (long long)m * P.qs_m + c8));
+      }
+      *(uint4*)(Qs + r * pitch + c8) = v;
+    }
+  } else {
+    for (int idx = tid; idx < LM_ROWS * KR; idx += LM_THREADS) {
+      const int r = idx / KR, i = idx - r * KR;
+      const int tq = r / G.HB, hh = r - tq * G.HB;
+      __nv_bfloat16 v = __float2bfloat16_rn(0.f);
+      if (tq < ntok && hh < HB) v = q_lat[(size_t)((h0 + hh) * P.qs_h + (long long)((size_t)b * P.Tn + t0 + tq) * P.qs_m + i)];
+      Qs[r * pitch + i] = v;
+    }
+  }
+  {
+    const int npair = (G.DKP - KR + 1) / 2;      // the rotary part and the zero padding behind it, two columns at a time
+    for (int idx = tid; idx < LM_ROWS * npair; idx += LM_THREADS) {
+      const int r = idx / npair, d = 2 * (idx - r * npair);
+      const int tq = r / G.HB, hh = r - tq * G.HB;
+      float v0 = 0.f, v1 = 0.f;
+      if (tq < ntok && hh < HB && d < R) {
+        const size_t m = (size_t)b * P.Tn + t0 + tq;
         const __nv_bfloat16* qr = proj + m * P.proj_stride + P.q_rot_col0 + (size_t)(h0 + hh) * P.q_head_stride;
-        if ((d | 1) < P.rot_dims) {
-          const float* cs = P.rope + (size_t)P.pos_ids[t0 + tq] * P.rot_dims + (d & ~1);
-          const float u = __bfloat162float(qr[d & ~1]), w = __bfloat162float(qr[d | 1]);
-          v = (d & 1) ? (w * cs[0] + u * cs[1]) : (u * cs[0] - w * cs[1]);
+        const float u = __bfloat162float(qr[d]), w = (d + 1 < R) ? __bfloat162float(qr[d + 1]) : 0.f;
+        if (d + 1 < P.rot_dims) {
+          const float* cs = P.rope + (size_t)P.pos_ids[t0 + tq] * P.rot_dims + d;
+          v0 = u * cs[0] - w * cs[1];
+          v1 = w * cs[0] + u * cs[1];
         } else {
-          v = __bfloat162float(qr[d]);
+          v0 = u;
+          v1 = w;
         }
       }
+      if (KR + d < G.DKP) Qs[r * pitch + KR + d] = __float2bfloat16_rn(v0);
+      if (KR + d + 1 < G.DKP) Qs[r * pitch + KR + d + 1] = __float2bfloat16_rn(v1);
     }
-    Qs[r * pitch + i] = __float2bfloat16_rn(v);
   }
   // zero the padding columns of the key rows once (the loads below never touch them)
-  for (int idx = tid; idx < LM_KC * (G.DKP - Dk); idx += LM_THREADS) {
+  for (int idx = tid; idx < 2 * LM_KC * (G.DKP - Dk); idx += LM_THREADS) {
     const int r = idx / (G.DKP - Dk), i = Dk + idx - r * (G.DKP - Dk);
-    Ks[r * pitch + i] = __float2bfloat16_rn(0.f);
+    Ks0[r * pitch + i] = __float2bfloat16_rn(0.f);
   }
 
   const int p_first = P.pos_ids[t0], p_last = P.pos_ids[t0 + ntok - 1];
@@ -309,34 +332,62 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
   const int wcol0 = warp * NTW * 8;            // this warp's first output column
   __syncthreads();
 
-  for (int j0 = j_begin; j0 < j_end; j0 += LM_KC) {
+  // rows j0 .. j0 + 63 of the cache into one of the two stages (16-byte asynchronous copies when rows allow)
+  auto load_keys = [&](int stage, int j0) {
+    __nv_bfloat16* dst = Ks0 + stage * LM_KC * pitch;
     const int nk = min(LM_KC, j_end - j0);
     if (vec) {
       const int cpr = Dk / 8;
       for (int ch = tid; ch < LM_KC * cpr; ch += LM_THREADS) {
         const int jj = ch / cpr, c8 = (ch - jj * cpr) * 8;
         const bool ok = jj < nk;
-        la_cp_async16(Ks + jj * pitch + c8, cache + (size_t)((ok ? j0 + jj : j0) % P.cache_len) * Dk + c8, ok);
+        la_cp_async16(dst + jj * pitch + c8, cache + (size_t)((ok ? j0 + jj : j0) % P.cache_len) * Dk + c8, ok);
       }
-      asm volatile("cp.async.commit_group;" ::: "memory");
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else {
       for (int idx = tid; idx < LM_KC * Dk; idx += LM_THREADS) {
         const int jj = idx / Dk, i = idx - jj * Dk;
-        Ks[jj * pitch + i] = jj < nk ? cache[(size_t)((j0 + jj) % P.cache_len) * Dk + i] : __float2bfloat16_rn(0.f);
+        dst[jj * pitch + i] = jj < nk ? cache[(size_t)((j0 + jj) % P.cache_len) * Dk + i] : __float2bfloat16_rn(0.f);
       }
     }
-    __syncthreads();
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  if (j_begin < j_end) load_keys(0, j_begin);
+  int stage = 0;
+  for (int j0 = j_begin; j0 < j_end; j0 += LM_KC, stage ^= 1) {
+    const int nk = min(LM_KC, j_end - j0);
+    const __nv_bfloat16* Ks = Ks0 + stage * LM_KC * pitch;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();            // this chunk has landed; every warp is done with the other stage, with Ss and with Ps
+    if (j0 + LM_KC < j_end) load_keys(stage ^ 1, j0 + LM_KC);     // the next chunk travels under this chunk's math
     {   // S = Q K^T: warp -> m-tile (warp & 1), key columns (warp >> 1) * 16 .. + 15
       const int mt = warp & 1, np = warp >> 1;
-      float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-      for (int ks = 0; ks < G.DKP / 16; ++ks) {
-        uint32_t af[4], bf[4];
-        la_ldmatrix_x4(af, Qs + (mt * 16 + (lane & 15)) * pitch + ks * 16 + (lane >> 4) * 8);
-        la_ldmatrix_x4(bf, Ks + (np * 16 + (lane & 7) + (lane >> 4) * 8) * pitch + ks * 16 + ((lane >> 3) & 1) * 8);
-        mma_bf16_16816(sacc[0], af[0], af[1], af[2], af[3], bf[0], bf[1]);
-        mma_bf16_16816(sacc[1], af[0], af[1], af[2], af[3], bf[2], bf[3]);
+      float part[4][2][4];     // four interleaved slices of the k range: independent accumulation chains, summed below
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int q = 0; q < 4; ++q) part[c][j][q] = 0.f;
+      const int nks = G.DKP / 16;
+      for (int ks0 = 0; ks0 < nks; ks0 += 4) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int ks = ks0 + c;
+          if (ks < nks) {
+            uint32_t af[4], bf[4];
+            la_ldmatrix_x4(af, Qs + (mt * 16 + (lane & 15)) * pitch + ks * 16 + (lane >> 4) * 8);
+            la_ldmatrix_x4(bf, Ks + (np * 16 + (lane & 7) + (lane >> 4) * 8) * pitch + ks * 16 + ((lane >> 3) & 1) * 8);
+            mma_bf16_16816(part[c][0], af[0], af[1], af[2], af[3], bf[0], bf[1]);
+            mma_bf16_16816(part[c][1], af[0], af[1], af[2], af[3], bf[2], bf[3]);
+          }
+        }
       }
+      float sacc[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) sacc[j][q] = (part[0][j][q] + part[1][j][q]) + (part[2][j][q] + part[3][j][q]);
 #pragma unroll
       for (int j = 0; j < 2; ++j)
 #pragma unroll
@@ -398,7 +449,6 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
         }
       }
     }
-    __syncthreads();
   }
 
   __nv_bfloat16* out = (__nv_bfloat16*)P.out;
@@ -431,7 +481,7 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
 }
 
 static size_t latent_mma_smem(int pitch) {
-  return sizeof(__nv_bfloat16) * ((size_t)(LM_ROWS + LM_KC) * pitch + (size_t)LM_ROWS * (LM_KC + 8)) +
+  return sizeof(__nv_bfloat16) * ((size_t)(LM_ROWS + 2 * LM_KC) * pitch + (size_t)LM_ROWS * (LM_KC + 8)) +
          sizeof(float) * ((size_t)LM_ROWS * (LM_KC + 1) + 3 * LM_ROWS) + sizeof(int) * LM_ROWS;
 }
 
@@ -557,7 +607,7 @@ int ll_latent_attn(const void* q_lat, long long qs_h, long long qs_m, const void
     if (G.TQ < 1) G.TQ = 1;
     G.DKP = (Dk + 15) / 16 * 16;
     G.pitch = G.DKP + 8;
-    if (latent_mma_smem(G.pitch) <= 200 * 1024) {
+    if (latent_mma_smem(G.pitch) <= 220 * 1024) {
       const int cols_per_warp = (kv_rank + 7) / 8;
       int rc;
       if (cols_per_warp <= 8) rc = launch_latent_mma<1>(P, G, B, st);

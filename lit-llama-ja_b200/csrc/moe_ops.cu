@@ -14,6 +14,7 @@ namespace llb {
 
 constexpr int RT_TOK = 4;        // tokens per routing block
 constexpr int RT_THREADS = 256;
+constexpr int RT_EG = 4;         // experts a warp accumulates side by side
 
 template <typename T>
 __global__ void __launch_bounds__(RT_THREADS) moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w_router,
@@ -29,21 +30,32 @@ __global__ void __launch_bounds__(RT_THREADS) moe_route_kernel(const T* __restri
   for (int idx = tid; idx < nt * dim; idx += RT_THREADS) xs[idx] = dt<T>::ld(x, (size_t)m0 * dim + idx);
   for (int idx = nt * dim + tid; idx < RT_TOK * dim; idx += RT_THREADS) xs[idx] = 0.f;
   __syncthreads();
-  for (int e = warp; e < X; e += RT_THREADS / 32) {
-    const float* wr = w_router + (size_t)e * dim;
-    float a[RT_TOK];
+  // RT_EG experts at a time per warp and four columns per step: 16 independent weight loads in flight per lane
+  for (int e0 = warp * RT_EG; e0 < X; e0 += (RT_THREADS / 32) * RT_EG) {
+    float a[RT_EG][RT_TOK];
 #pragma unroll
-    for (int t = 0; t < RT_TOK; ++t) a[t] = 0.f;
+    for (int g = 0; g < RT_EG; ++g)
+#pragma unroll
+      for (int t = 0; t < RT_TOK; ++t) a[g][t] = 0.f;
+#pragma unroll 4
     for (int i = lane; i < dim; i += 32) {
-      const float w = wr[i];
+      float w[RT_EG];
 #pragma unroll
-      for (int t = 0; t < RT_TOK; ++t) a[t] += w * xs[t * dim + i];
+      for (int g = 0; g < RT_EG; ++g) w[g] = w_router[(size_t)min(e0 + g, X - 1) * dim + i];
+#pragma unroll
+      for (int t = 0; t < RT_TOK; ++t) {
+        const float xv = xs[t * dim + i];
+#pragma unroll
+        for (int g = 0; g < RT_EG; ++g) a[g][t] += w[g] * xv;
+      }
     }
 #pragma unroll
-    for (int t = 0; t < RT_TOK; ++t) {
-      const float s = warp_sum(a[t]);
-      if (lane == 0) zs[t * X + e] = s + (bias ? bias[e] : 0.f);
-    }
+    for (int g = 0; g < RT_EG; ++g)
+#pragma unroll
+      for (int t = 0; t < RT_TOK; ++t) {
+        const float sum = warp_sum(a[g][t]);
+        if (lane == 0 && e0 + g < X) zs[t * X + e0 + g] = sum + (bias ? bias[e0 + g] : 0.f);
+      }
   }
   __syncthreads();
   if (warp < nt) {

@@ -71,6 +71,8 @@ class LatentAttention(nn.Module):
         self.gate_col0 = self.q_cols
         self.kv_col0 = self.q_cols + s.heads
         n_in = self.kv_col0 + (s.row if self.owns_cache else 0)
+        self.n_in = n_in
+        n_in = (n_in + 7) // 8 * 8          # rows of zeros up to a multiple of 8: the library's fast GEMMs want aligned outputs
         kw = dict(dtype=dtype, device=device)
         self.w_in = nn.Parameter(torch.empty((n_in, s.width), **kw), requires_grad=False)          # [W_q; W_g; W_dkv]
         self.w_uk = nn.Parameter(torch.empty((s.heads, s.nope_dim, s.kv_rank), **kw), requires_grad=False)
@@ -83,7 +85,8 @@ class LatentAttention(nn.Module):
         """``get(suffix)`` returns the tensor '<layer>.mix.<suffix>' ([out, in] for the Linears)."""
         s = self.spec
         parts = [get("q"), get("g")] + ([get("dkv")] if self.owns_cache else [])
-        self.w_in.copy_(torch.cat([p.to(self.w_in.dtype) for p in parts], dim=0))
+        self.w_in.zero_()
+        self.w_in[: self.n_in].copy_(torch.cat([p.to(self.w_in.dtype) for p in parts], dim=0))
         self.w_uk.copy_(get("uk").reshape(s.heads, s.nope_dim, s.kv_rank))
         self.w_uv_t.copy_(get("uv").reshape(s.heads, s.v_dim, s.kv_rank).transpose(1, 2))
         self.w_o.copy_(get("o"))

@@ -162,7 +162,7 @@ class Lepalorn(nn.Module):
         self.embed = nn.Parameter(torch.empty((config.vocab, config.width), **kw), requires_grad=False)
         self.blocks = nn.ModuleList(LepalornBlock(i, l, dtype, self.device) for i, l in enumerate(config.layers))
         self.final_norm = nn.Parameter(torch.ones(1, dtype=torch.float32, device=self.device), requires_grad=False)
-        self.head = nn.Parameter(torch.empty((config.vocab, config.width), **kw), requires_grad=False)
+        self.head = nn.Parameter(torch.zeros(((config.vocab + 7) // 8 * 8, config.width), **kw), requires_grad=False)   # zero rows to 8
         self._pool = TensorPool(max_sets=2, on_evict=self._drop_graphs)
         self._rope: Dict[Tuple[float, int], torch.Tensor] = {}
         self._rope_len = 0
@@ -188,7 +188,7 @@ class Lepalorn(nn.Module):
     def load_tensors(self, get) -> None:
         """``get(name)`` returns the checkpoint tensor of that name (any float dtype, CPU or GPU)."""
         self.embed.copy_(get("embed"))
-        self.head.copy_(get("head"))
+        self.head[: self.config.vocab].copy_(get("head"))
         self.final_norm.copy_(get("final.norm").float().reshape(1))
         for b in self.blocks:
             b.load(get)
@@ -319,7 +319,7 @@ class Lepalorn(nn.Module):
         for i, blk in enumerate(self.blocks):
             spec = blk.mix.spec
             span = spec.window if spec.window is not None else self._ring
-            splits = max(1, min(16, (2 * sms) // max(1, M * ((spec.heads + 7) // 8)), (min(span, self._ring) + 127) // 128))
+            splits = max(1, min(16, (2 * sms) // max(1, M * ((spec.heads + 31) // 32)), (min(span, self._ring) + 63) // 64))
             rope = self._rope[(spec.rot_base, spec.rot_dims)]
             y = blk.mix(x_act, B, T, pos_ids, rope, self.kv_caches[self._cache_of[i]], splits)
             nxt = mixed[i & 1]
@@ -346,4 +346,4 @@ class Lepalorn(nn.Module):
             logits = xn @ self.head.t()
         else:
             logits = torch.mm(xn, self.head.t(), out_dtype=torch.float32)
-        return logits.view(B, -1, cfg.vocab)
+        return logits[:, : cfg.vocab].reshape(B, -1, cfg.vocab)

@@ -55,7 +55,7 @@ class MoE(nn.Module):
         self.w_gu = nn.Parameter(torch.empty((s.experts, 2 * s.ff, s.width), **kw), requires_grad=False)
         self.w_down = nn.Parameter(torch.empty((s.experts, s.width, s.ff), **kw), requires_grad=False)
         if s.shared_ff:
-            rows = 2 * s.shared_ff + (1 if s.shared_gate else 0)
+            rows = (2 * s.shared_ff + (1 if s.shared_gate else 0) + 7) // 8 * 8     # zero rows up to a multiple of 8
             self.w_shared_in = nn.Parameter(torch.empty((rows, s.width), **kw), requires_grad=False)   # [gate; up; sg]
             self.w_shared_down = nn.Parameter(torch.empty((s.width, s.shared_ff), **kw), requires_grad=False)
 
@@ -71,10 +71,11 @@ class MoE(nn.Module):
             self.w_down[e].copy_(get(f"e{e}.down"))
         if s.shared_ff:
             f = s.shared_ff
+            self.w_shared_in.zero_()
             self.w_shared_in[:f].copy_(get("shared.gate"))
             self.w_shared_in[f:2 * f].copy_(get("shared.up"))
             if s.shared_gate:
-                self.w_shared_in[2 * f:].copy_(get("shared.sg").reshape(1, s.width))
+                self.w_shared_in[2 * f:2 * f + 1].copy_(get("shared.sg").reshape(1, s.width))
             self.w_shared_down.copy_(get("shared.down"))
 
     def route(self, x_act: torch.Tensor):

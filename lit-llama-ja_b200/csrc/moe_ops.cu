@@ -30,6 +30,7 @@ __global__ void __launch_bounds__(RT_THREADS) moe_route_kernel(const T* __restri
   for (int idx = tid; idx < nt * dim; idx += RT_THREADS) xs[idx] = dt<T>::ld(x, (size_t)m0 * dim + idx);
   for (int idx = nt * dim + tid; idx < RT_TOK * dim; idx += RT_THREADS) xs[idx] = 0.f;
   __syncthreads();
+  const bool vec4 = (dim % 4 == 0) && (((uintptr_t)w_router & 15) == 0);
   // RT_EG experts at a time per warp and four columns per step: 16 independent weight loads in flight per lane
   for (int e0 = warp * RT_EG; e0 < X; e0 += (RT_THREADS / 32) * RT_EG) {
     float a[RT_EG][RT_TOK];
@@ -37,16 +38,31 @@ __global__ void __launch_bounds__(RT_THREADS) moe_route_kernel(const T* __restri
     for (int g = 0; g < RT_EG; ++g)
 #pragma unroll
       for (int t = 0; t < RT_TOK; ++t) a[g][t] = 0.f;
+    if (vec4) {          // 16-byte weight loads, four steps unrolled: 16 independent loads in flight per lane
 #pragma unroll 4
-    for (int i = lane; i < dim; i += 32) {
-      float w[RT_EG];
+      for (int i4 = lane; i4 < dim / 4; i4 += 32) {
+        float4 w[RT_EG];
 #pragma unroll
-      for (int g = 0; g < RT_EG; ++g) w[g] = w_router[(size_t)min(e0 + g, X - 1) * dim + i];
+        for (int g = 0; g < RT_EG; ++g) w[g] = ((const float4*)(w_router + (size_t)min(e0 + g, X - 1) * dim))[i4];
 #pragma unroll
-      for (int t = 0; t < RT_TOK; ++t) {
-        const float xv = xs[t * dim + i];
+        for (int t = 0; t < RT_TOK; ++t) {
+          const float4 xv = ((const float4*)(xs + t * dim))[i4];
 #pragma unroll
-        for (int g = 0; g < RT_EG; ++g) a[g][t] += w[g] * xv;
+          for (int g = 0; g < RT_EG; ++g) a[g][t] += w[g].x * xv.x + w[g].y * xv.y + w[g].z * xv.z + w[g].w * xv.w;
+        }
+      }
+    } else {
+#pragma unroll 4
+      for (int i = lane; i < dim; i += 32) {
+        float w[RT_EG];
+#pragma unroll
+        for (int g = 0; g < RT_EG; ++g) w[g] = w_router[(size_t)min(e0 + g, X - 1) * dim + i];
+#pragma unroll
+        for (int t = 0; t < RT_TOK; ++t) {
+          const float xv = xs[t * dim + i];
+#pragma unroll
+          for (int g = 0; g < RT_EG; ++g) a[g][t] += w[g] * xv;
+        }
       }
     }
 #pragma unroll

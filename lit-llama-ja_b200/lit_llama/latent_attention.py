@@ -59,6 +59,8 @@ def build_rope_table(n_pos: int, rot_dims: int, base: float, device) -> torch.Te
     i = torch.arange(rot_dims // 2, dtype=torch.float64)
     freq = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / max(rot_dims, 1))
     ang = torch.arange(n_pos, dtype=torch.float64)[:, None] * freq[None]
+    if rot_dims == 0:                       # nothing turns: a table the kernels never index, but a valid address
+        return torch.zeros((n_pos, 1, 2), dtype=torch.float32, device=device)
     return torch.stack((ang.cos(), ang.sin()), dim=-1).float().contiguous().to(device)
 
 

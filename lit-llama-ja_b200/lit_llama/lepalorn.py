@@ -345,5 +345,8 @@ class Lepalorn(nn.Module):
         if self.dtype == torch.float32:
             logits = xn @ self.head.t()
         else:
-            logits = torch.mm(xn, self.head.t(), out_dtype=torch.float32)
+            try:
+                logits = torch.mm(xn, self.head.t(), out_dtype=torch.float32)
+            except RuntimeError:           # a width the library's mixed-output GEMM does not take: fp32 product of the same operands
+                logits = xn.float() @ self.head.float().t()
         return logits[:, : cfg.vocab].reshape(B, -1, cfg.vocab)

@@ -1,5 +1,5 @@
 """One prefill and a few single-token steps of a Lepalorn of real layer shapes (random weights): the workload the ncu
-captures of profiles/r03_lepalorn_*.md were taken on.  python profiles/lepalorn_probe.py [size] [prompt_len] [steps]"""
+captures of profiles/lepalorn_kernels.md were taken on.  python profiles/lepalorn_probe.py [size] [prompt_len] [steps]"""
 import sys
 from pathlib import Path
 

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from oracle import lepalorn as O
-from tests.util_lepalorn import RMS_TOL, TOL, agrees, case_mixed, case_ones, load, rel_err, rms_err, run_schedule, write_model
+from tests.util_lepalorn import RMS_TOL, TOL, agrees, case_mixed, case_odd, case_ones, load, rel_err, rms_err, run_schedule, write_model
 
 pytestmark = pytest.mark.gpu
 
@@ -102,6 +102,17 @@ def test_sizes_that_are_one(ones, dtype):
     m = load(folder, dtype)
     assert agrees(run_schedule(m, toks, [len(toks)], 32)[0], want, dtype)
     assert agrees(run_schedule(m, toks, [2, 1, 1, 9, 1, 1, 1, 7], 32)[0], want, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sizes_that_are_multiples_of_nothing(tmp_path, dtype):
+    cfg, W = case_odd()
+    folder = write_model(tmp_path / "odd", cfg, W)
+    toks = np.random.RandomState(12).randint(0, cfg["vocab"], size=31).tolist()
+    want = O.forward(cfg, W, toks)
+    m = load(folder, dtype, prefill_portion=5)
+    assert agrees(run_schedule(m, toks, [len(toks)], 40)[0], want, dtype)
+    assert agrees(run_schedule(m, toks, [2, 3, 9, 1, 1, 1, 14], 40)[0], want, dtype)
 
 
 def test_long_decoding_through_several_ring_lengths(mixed):

@@ -36,6 +36,16 @@ def case_ones(seed=1):
     return cfg, O.random_weights(cfg, seed, shared_gate=False)
 
 
+def case_odd(seed=2):
+    """Nothing is a multiple of 8 (or of 4): every kernel takes its unaligned path."""
+    layers = [
+        (O.mixer_cfg(5, 5, 6, 7, 13, 11, base=77.0), O.mlp_cfg(3, 2, 11, 0.9, 5, 0.7)),
+        (O.mixer_cfg(3, 7, 6, 3, 13, 3, base=77.0, kv_from=0), O.mlp_cfg(7, 3, 9, 1.1)),
+    ]
+    cfg = O.model_cfg(37, 50, layers, eps=1e-6, embedding_scale=2.5)
+    return cfg, O.random_weights(cfg, seed)
+
+
 def write_model(folder, cfg, W):
     from lit_llama.safetensors_io import save_safetensors
 

@@ -419,6 +419,16 @@ LL_API int ll_moe_grouped_gemm(const void* a, int lda, const void* w, const int3
                                int dtype, int n_rows, int top, int n_experts, int N, int K, float limit, float alpha,
                                void* c, int ldc, ll_stream stream);
 
+/* The same grouped GEMM on the tcgen05 tensor cores (bf16, TMA-tiled operands, accumulators in TMEM), for steps with
+ * many rows per expert.  a [n_rows][K] holds the rows ALREADY in sorted order (mode 1: gather them with
+ * ll_moe_gather_rows: out[r] = x[perm[r] / top]); w, offsets, perm, mode, c as in ll_moe_grouped_gemm.  K a multiple of 8,
+ * operands 16-byte aligned.  ll_moe_tc_error(): 0, or the code of the first bounded wait that ran out inside these
+ * kernels since the library was loaded (synchronises the device). */
+LL_API int ll_moe_gather_rows(const void* x, int ldx, const int32_t* perm, int top, int n_rows, int K, void* out, ll_stream stream);
+LL_API int ll_moe_grouped_gemm_tc(const void* a, const void* w, const int32_t* offsets, const int32_t* perm, int mode, int n_rows,
+                                  int n_experts, int N, int K, float limit, float alpha, void* c, int ldc, ll_stream stream);
+LL_API int ll_moe_tc_error(void);
+
 /* out[m] = sum_k expert_w[m][k] * y[m * top + k]  (+ sigmoid(shared_gate[m * gate_ld]) * shared_y[m], when shared_y is
  * given; shared_gate NULL: the shared expert is added as it is). */
 LL_API int ll_moe_combine(const void* y, const float* expert_w, int top, const void* shared_y, int shared_ld,

@@ -167,14 +167,24 @@ def kernel_table(s, lep, device, timer, prompt_len):
         h = torch.empty((n, s["ff"]), dtype=bf, device=device)
         yy = torch.empty((n, E), dtype=bf, device=device)
 
+        tc = moe.takes_tensor_cores(n, x)         # the path the module takes for a step of this size
+        xs = torch.empty((n, E), dtype=bf, device=device) if tc else None
+
         def experts():
+            if tc:
+                N.call("ll_moe_gather_rows", N.ptr(x), E, N.ptr(perm), s["top"], n, E, N.ptr(xs), N.stream())
+                N.call("ll_moe_grouped_gemm_tc", N.ptr(xs), N.ptr(moe.w_gu), N.ptr(offsets), N.ptr(perm), 1, n, s["experts"], s["ff"], E,
+                       7.0, 1.702, N.ptr(h), s["ff"], N.stream())
+                N.call("ll_moe_grouped_gemm_tc", N.ptr(h), N.ptr(moe.w_down), N.ptr(offsets), N.ptr(perm), 0, n, s["experts"], E, s["ff"],
+                       0.0, 0.0, N.ptr(yy), E, N.stream())
+                return
             N.call("ll_moe_grouped_gemm", N.ptr(x), E, N.ptr(moe.w_gu), N.ptr(offsets), N.ptr(perm), 1, N.LL_BF16, n, s["top"], s["experts"],
                    s["ff"], E, 7.0, 1.702, N.ptr(h), s["ff"], N.stream())
             N.call("ll_moe_grouped_gemm", N.ptr(h), s["ff"], N.ptr(moe.w_down), N.ptr(offsets), N.ptr(perm), 0, N.LL_BF16, n, s["top"],
                    s["experts"], E, s["ff"], 0.0, 0.0, N.ptr(yy), E, N.stream())
 
         used = min(s["experts"], n)
-        add(f"moe grouped GEMMs {tag}", timer(experts), 2.0 * n * 3 * s["ff"] * E, 2.0 * used * 3 * s["ff"] * E)
+        add(f"moe grouped GEMMs {tag}" + (" (tcgen05, with the row gather)" if tc else ""), timer(experts), 2.0 * n * 3 * s["ff"] * E, 2.0 * used * 3 * s["ff"] * E)
         nh = s["top"] * s["ff"] + s["shared"]
         w1, w2 = torch.randn((2 * nh, E), device=device, dtype=bf), torch.randn((E, nh), device=device, dtype=bf)
         hh = torch.empty((T, nh), device=device, dtype=bf)

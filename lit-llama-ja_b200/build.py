@@ -26,7 +26,7 @@ def needs_build():
     if not OUT.exists():
         return True
     t = OUT.stat().st_mtime
-    deps = list(CSRC.glob("*")) + [HERE.parent / "include" / "llb200.h"]
+    deps = [p for p in CSRC.glob("*") if p.suffix in (".cu", ".cuh", ".h")] + [HERE.parent / "include" / "llb200.h"]
     return any(p.stat().st_mtime > t for p in deps)
 
 
@@ -60,7 +60,7 @@ def build_only(name, stems, verbose=False):
     what a model family needs, without waiting for the kernels of the others.  Rebuilt only when a source is newer."""
     out = HERE / "lit_llama" / f"libllb200_{name}.so"
     srcs = [CSRC / f"{s}.cu" for s in stems]
-    deps = srcs + [CSRC / "common.cuh", HERE.parent / "include" / "llb200.h"]
+    deps = srcs + list(CSRC.glob("*.cuh")) + [HERE.parent / "include" / "llb200.h"]
     if out.exists() and all(p.stat().st_mtime <= out.stat().st_mtime for p in deps):
         return out
     objdir = CSRC / f"_obj_{name}"

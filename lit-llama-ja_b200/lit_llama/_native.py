@@ -116,6 +116,9 @@ EXPORTS = {
     "ll_latent_attn_scratch_bytes": ([i32, i32, i32, i32], sz_t),
     "ll_moe_route": ([vp, i32, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp], C.c_int),
     "ll_moe_grouped_gemm": ([vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, C.c_float, C.c_float, vp, i32, vp], C.c_int),
+    "ll_moe_gather_rows": ([vp, i32, vp, i32, i32, i32, vp, vp], C.c_int),
+    "ll_moe_grouped_gemm_tc": ([vp, vp, vp, vp, i32, i32, i32, i32, i32, C.c_float, C.c_float, vp, i32, vp], C.c_int),
+    "ll_moe_tc_error": ([], C.c_int),
     "ll_moe_combine": ([vp, vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, vp], C.c_int),
 }
 _fn = {name: _proto(name, a, r) for name, (a, r) in EXPORTS.items()}
@@ -141,6 +144,11 @@ def call(name: str, *args) -> None:
     global LAUNCHES
     check(_fn[name](*args), name)
     LAUNCHES += 1
+
+
+def has(name: str) -> bool:
+    """Whether the loaded library exports ``name`` (a reduced build lacks the kernels it was not built for)."""
+    return hasattr(lib, name)
 
 
 def call_ret(name: str, *args):

@@ -6,10 +6,14 @@
 
 The experts' weights are stacked ([X, 2 ff, width] for [gate; up], [X, width, ff] for down) and run as two grouped GEMMs
 over the (token, choice) pairs sorted by expert; counts, offsets and the permutation never leave the device, so a step
-is one fixed launch sequence.  The shared expert is dense (library GEMMs) with its gate logit as one more output row.
+is one fixed launch sequence.  Steps with many rows per expert (prefill in bfloat16) gather the rows into sorted order
+and run both GEMMs on the tcgen05 tensor cores (TMA-tiled operands, accumulators in TMEM, the gated unit as the first
+GEMM's epilogue); small steps use the mma.sync / FMA kernels that take rows in place.  The shared expert is dense
+(library GEMMs) with its gate logit as one more output row.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -18,6 +22,10 @@ import torch.nn as nn
 from torch.nn import functional as F
 
 from . import _native as N
+
+# the tcgen05 path: at least this many (token, choice) rows in the step, and on average per expert
+TC_MIN_ROWS = int(os.environ.get("LLB200_MOE_TC_MIN_ROWS", "1024"))
+TC_MIN_ROWS_PER_EXPERT = int(os.environ.get("LLB200_MOE_TC_MIN_ROWS_PER_EXPERT", "48"))
 
 
 @dataclass
@@ -91,6 +99,13 @@ class MoE(nn.Module):
                s.experts, s.top, N.ptr(idx), N.ptr(w), N.ptr(counts), N.ptr(rank), N.ptr(offsets), N.ptr(perm), N.stream())
         return idx, w, offsets, perm
 
+    def takes_tensor_cores(self, n_rows: int, x_act: torch.Tensor) -> bool:
+        """Whether a step of ``n_rows`` (token, choice) rows runs its expert GEMMs on the tcgen05 kernels: bfloat16, rows
+        that TMA can tile (16-byte multiples), and enough rows per expert to fill 128-row tiles."""
+        s = self.spec
+        return (x_act.dtype == torch.bfloat16 and s.width % 8 == 0 and s.ff % 8 == 0 and x_act.stride(0) % 8 == 0
+                and n_rows >= TC_MIN_ROWS and n_rows >= TC_MIN_ROWS_PER_EXPERT * s.experts and N.has("ll_moe_grouped_gemm_tc"))
+
     def forward(self, x_act: torch.Tensor) -> torch.Tensor:
         s = self.spec
         M, dev, dtype = x_act.shape[0], x_act.device, x_act.dtype
@@ -98,11 +113,19 @@ class MoE(nn.Module):
         _, w, offsets, perm = self.route(x_act)
         n = M * s.top
         h = torch.empty((n, s.ff), dtype=dtype, device=dev)
-        N.call("ll_moe_grouped_gemm", N.ptr(x_act), x_act.stride(0), N.ptr(self.w_gu), N.ptr(offsets), N.ptr(perm), 1, dt, n,
-               s.top, s.experts, s.ff, s.width, float(s.limit), float(s.alpha), N.ptr(h), s.ff, st)
         y = torch.empty((n, s.width), dtype=dtype, device=dev)
-        N.call("ll_moe_grouped_gemm", N.ptr(h), s.ff, N.ptr(self.w_down), N.ptr(offsets), N.ptr(perm), 0, dt, n, s.top, s.experts,
-               s.width, s.ff, 0.0, 0.0, N.ptr(y), s.width, st)
+        if self.takes_tensor_cores(n, x_act):
+            xs = torch.empty((n, s.width), dtype=dtype, device=dev)
+            N.call("ll_moe_gather_rows", N.ptr(x_act), x_act.stride(0), N.ptr(perm), s.top, n, s.width, N.ptr(xs), st)
+            N.call("ll_moe_grouped_gemm_tc", N.ptr(xs), N.ptr(self.w_gu), N.ptr(offsets), N.ptr(perm), 1, n, s.experts, s.ff, s.width,
+                   float(s.limit), float(s.alpha), N.ptr(h), s.ff, st)
+            N.call("ll_moe_grouped_gemm_tc", N.ptr(h), N.ptr(self.w_down), N.ptr(offsets), N.ptr(perm), 0, n, s.experts, s.width, s.ff,
+                   0.0, 0.0, N.ptr(y), s.width, st)
+        else:
+            N.call("ll_moe_grouped_gemm", N.ptr(x_act), x_act.stride(0), N.ptr(self.w_gu), N.ptr(offsets), N.ptr(perm), 1, dt, n,
+                   s.top, s.experts, s.ff, s.width, float(s.limit), float(s.alpha), N.ptr(h), s.ff, st)
+            N.call("ll_moe_grouped_gemm", N.ptr(h), s.ff, N.ptr(self.w_down), N.ptr(offsets), N.ptr(perm), 0, dt, n, s.top, s.experts,
+                   s.width, s.ff, 0.0, 0.0, N.ptr(y), s.width, st)
         ys = gate = None
         gate_ld = 0
         if s.shared_ff:

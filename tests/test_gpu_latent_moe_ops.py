@@ -213,3 +213,35 @@ def test_router_permutation_and_grouped_experts(dtype, shape):
     for e in range(X):
         assert all(flat[p] == e for p in pm[off[e]:off[e + 1]])
     close(host(moe(dev(h, dtype))), O.moe(h, {k: np.asarray(v, dtype=np.float64) for k, v in W.items()}, "l0.mlp.", cfgf), TOL[dtype] * 3)
+
+
+@pytest.mark.parametrize("shape", [(1500, 64, 5, 2, 72), (700, 320, 3, 3, 40), (1100, 200, 7, 2, 136), (2300, 512, 4, 1, 264)])
+def test_grouped_experts_on_the_tcgen05_path(shape, monkeypatch):
+    """Many rows per expert: the tensor-core kernels (row tiles of 128 that run past an expert's last row, an output
+    width that is no multiple of the tile, a K that is no multiple of 64, an empty expert) against the float64 oracle
+    and against the kernels that small steps take."""
+    import lit_llama.moe as MOE
+    from lit_llama import _native as N
+
+    M, width, X, top, ff = shape
+    r = np.random.RandomState(11)
+    cfgf = O.mlp_cfg(X, top, ff, 0.6, 9, 0.9)
+    mc = O.model_cfg(8, width, [(O.mixer_cfg(1, 2, 2, 2, 2, 2), cfgf)])
+    W = O.random_weights(mc, 12)
+    if X > 4:
+        W["l0.mlp.router.b"][1] = -50.0                        # an empty segment between two full ones
+    moe = MOE.MoE(MOE.MoESpec(width, X, top, ff, 0.6, 9, 0.9), torch.bfloat16, "cuda")
+    moe.load(lambda s: dev(W["l0.mlp." + s], torch.bfloat16))
+    h = O.bf16_round(r.randn(M, width)).astype(np.float64)
+    x = dev(h, torch.bfloat16)
+    monkeypatch.setattr(MOE, "TC_MIN_ROWS", 256)
+    monkeypatch.setattr(MOE, "TC_MIN_ROWS_PER_EXPERT", 1)
+    assert moe.takes_tensor_cores(M * top, x)
+    got = host(moe(x))
+    assert N.call_ret("ll_moe_tc_error") == 0
+    monkeypatch.setattr(MOE, "TC_MIN_ROWS", 1 << 30)
+    assert not moe.takes_tensor_cores(M * top, x)
+    other = host(moe(x))
+    want = O.moe(h, {k: np.asarray(v, dtype=np.float64) for k, v in W.items()}, "l0.mlp.", cfgf)
+    close(got, want, TOL[torch.bfloat16] * 3)
+    close(got, other, 1e-2)

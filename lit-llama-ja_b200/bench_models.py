@@ -33,8 +33,17 @@ class Timer:
     def __init__(self, device):
         self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
 
-    def __call__(self, fn, iters=5, warmup=3):
+    def __call__(self, fn, iters=5, warmup=3, graph=False):
+        """Median device time of ``fn()`` with a cold L2.  ``graph``: ``fn`` is captured once and the timed region is one
+        graph launch, so that a sequence of short kernels is not timed at the pace the host issues it."""
         for _ in range(warmup):
+            fn()
+        if graph:
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            fn = g.replay
             fn()
         ts = []
         for _ in range(iters):
@@ -142,13 +151,13 @@ def kernel_table(s, lep, device, timer, prompt_len):
                    0.1, splits, N.ptr(scratch), N.stream())
 
         keys = sum(min(W, p + 1) for p in range(pos0, pos0 + T))
-        add(f"latent_attn {tag}", timer(attn), 2.0 * keys * H * (2 * KR + R), 2.0 * (min(W + T, pos0 + T) * (KR + R) + 2 * H * T * KR))
+        add(f"latent_attn {tag}", timer(attn, graph=True), 2.0 * keys * H * (2 * KR + R), 2.0 * (min(W + T, pos0 + T) * (KR + R) + 2 * H * T * KR))
         # LLaMA's attention at equal heads and head size = nope + rot
         hs = s["width"] // H
         q = torch.randn((1, H, T, hs), device=device, dtype=bf)
         if T > 1:
             k, v = torch.randn_like(q), torch.randn_like(q)
-            add("llama sdpa prefill (library, full causal)", timer(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True)),
+            add("llama sdpa prefill (library, full causal)", timer(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True), graph=True),
                 2.0 * (T * (T + 1) / 2) * H * 2 * hs, 2.0 * 4 * T * H * hs)
         elif hs in (32, 64, 128):
             S = prompt_len + 64
@@ -158,7 +167,7 @@ def kernel_table(s, lep, device, timer, prompt_len):
             sp = max(1, min(8, (2 * N._fn["ll_sm_count"]()) // H, (S + 63) // 64))
             ws = N.Workspace.get(device).ensure(attn_bytes=N.attn_scratch_bytes(1, H, hs, sp), attn_counters=H)
             add("llama decode_attn", timer(lambda: N.call("ll_decode_attn", N.ptr(q), N.ptr(kc), N.ptr(vc), N.ptr(p3), N.ptr(y), N.LL_BF16, 1,
-                                                          H, hs, S, sp, N.ptr(ws.attn_scratch), N.ptr(ws.attn_counters), 0, N.stream())),
+                                                          H, hs, S, sp, N.ptr(ws.attn_scratch), N.ptr(ws.attn_counters), 0, N.stream()), graph=True),
                 4.0 * (prompt_len + 1) * H * hs, 2.0 * 2 * (prompt_len + 1) * H * hs)
         # experts: both grouped GEMMs of the layer / LLaMA's three MLP GEMMs
         moe = blk.mlp
@@ -184,7 +193,7 @@ def kernel_table(s, lep, device, timer, prompt_len):
                    s["experts"], E, s["ff"], 0.0, 0.0, N.ptr(yy), E, N.stream())
 
         used = min(s["experts"], n)
-        add(f"moe grouped GEMMs {tag}" + (" (tcgen05, with the row gather)" if tc else ""), timer(experts), 2.0 * n * 3 * s["ff"] * E, 2.0 * used * 3 * s["ff"] * E)
+        add(f"moe grouped GEMMs {tag}" + (" (tcgen05, with the row gather)" if tc else ""), timer(experts, graph=True), 2.0 * n * 3 * s["ff"] * E, 2.0 * used * 3 * s["ff"] * E)
         nh = s["top"] * s["ff"] + s["shared"]
         w1, w2 = torch.randn((2 * nh, E), device=device, dtype=bf), torch.randn((E, nh), device=device, dtype=bf)
         hh = torch.empty((T, nh), device=device, dtype=bf)
@@ -193,7 +202,7 @@ def kernel_table(s, lep, device, timer, prompt_len):
             F.linear(x, w1)
             F.linear(hh, w2)
 
-        add(f"llama MLP GEMMs {tag} (library)", timer(mlp), 2.0 * T * 3 * nh * E, 2.0 * 3 * nh * E)
+        add(f"llama MLP GEMMs {tag} (library)", timer(mlp, graph=True), 2.0 * T * 3 * nh * E, 2.0 * 3 * nh * E)
     return rows, which
 
 

@@ -73,6 +73,42 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Row tile `t` of a grouped problem whose groups are the segments offsets[g] .. offsets[g + 1] of a sorted row space, every
+// group cut into tiles of `bm` rows: which group, its first row, and how many of the tile's rows belong to the group.
+// Called by one whole warp; 32 groups are examined per pass (two loads per lane in flight, a shuffle scan of the tile
+// counts), so the lookup costs a couple of memory round trips instead of one per group.  Lane 0 writes out[0..2] =
+// (group or -1 when t is past the last tile, first row, rows).
+__device__ __forceinline__ void grouped_tile_lookup(const int32_t* __restrict__ offsets, int n_groups, int t, int bm, int* out) {
+  const int lane = threadIdx.x & 31;
+  int before = 0;
+  bool found = false;
+  for (int g0 = 0; g0 < n_groups && !found; g0 += 32) {
+    const int g = g0 + lane;
+    const int o0 = g < n_groups ? offsets[g] : 0, o1 = g < n_groups ? offsets[g + 1] : 0;
+    const int tiles = (o1 - o0 + bm - 1) / bm;
+    int incl = tiles;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += v;
+    }
+    const int excl = before + incl - tiles;
+    const bool mine = g < n_groups && t >= excl && t < excl + tiles;
+    const unsigned ball = __ballot_sync(0xffffffffu, mine);
+    if (ball != 0u) {
+      found = true;
+      if (mine) {
+        const int r0 = o0 + (t - excl) * bm;
+        out[0] = g;
+        out[1] = r0;
+        out[2] = min(bm, o1 - r0);
+      }
+    }
+    before += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (!found && lane == 0) out[0] = -1;
+}
+
 // ------------------------------------------------------------------ PTX: mbarrier / TMA / PDL
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

@@ -263,48 +263,45 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
   }
   // queries: latent part as it is (16-byte pieces when rows allow), rotary part rotated in fp32, zero padding
   const bool qvec = (KR % 8 == 0) && (P.qs_h % 8 == 0) && (P.qs_m % 8 == 0) && (((uintptr_t)q_lat & 15) == 0);
-  if (qvec) {
-    const int cpr = KR / 8;
-    for (int ch = tid; ch < LM_ROWS * cpr; ch += LM_THREADS) {
-      const int r = ch / cpr, c8 = (ch - r * cpr) * 8;
-      const int tq = r / G.HB, hh = r - tq * G.HB;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (tq < ntok && hh < HB) {
-        const size_t m = (size_t)b * P.Tn + t0 + tq;
-        v = *(const uint4*)(q_lat + (size_t)((h0 + hh) * P.qs_h + (long long)m * P.qs_m + c8));
+  for (int r = warp; r < LM_ROWS; r += LM_THREADS / 32) {       // a row per warp pass, lanes along the row
+    const int tq = r / G.HB, hh = r - tq * G.HB;
+    const bool live = tq < ntok && hh < HB;
+    const __nv_bfloat16* src = q_lat + (size_t)((h0 + hh) * P.qs_h + (long long)((size_t)b * P.Tn + t0 + tq) * P.qs_m);
+    if (qvec) {
+      for (int c = lane; c < KR / 8; c += 32) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (live) v = *(const uint4*)(src + c * 8);
+        *(uint4*)(Qs + r * pitch + c * 8) = v;
       }
-      *(uint4*)(Qs + r * pitch + c8) = v;
-    }
-  } else {
-    for (int idx = tid; idx < LM_ROWS * KR; idx += LM_THREADS) {
-      const int r = idx / KR, i = idx - r * KR;
-      const int tq = r / G.HB, hh = r - tq * G.HB;
-      __nv_bfloat16 v = __float2bfloat16_rn(0.f);
-      if (tq < ntok && hh < HB) v = q_lat[(size_t)((h0 + hh) * P.qs_h + (long long)((size_t)b * P.Tn + t0 + tq) * P.qs_m + i)];
-      Qs[r * pitch + i] = v;
+    } else {
+      for (int i = lane; i < KR; i += 32) Qs[r * pitch + i] = live ? src[i] : __float2bfloat16_rn(0.f);
     }
   }
   {
     const int npair = (G.DKP - KR + 1) / 2;      // the rotary part and the zero padding behind it, two columns at a time
-    for (int idx = tid; idx < LM_ROWS * npair; idx += LM_THREADS) {
-      const int r = idx / npair, d = 2 * (idx - r * npair);
+    for (int r = warp; r < LM_ROWS; r += LM_THREADS / 32) {
       const int tq = r / G.HB, hh = r - tq * G.HB;
-      float v0 = 0.f, v1 = 0.f;
-      if (tq < ntok && hh < HB && d < R) {
-        const size_t m = (size_t)b * P.Tn + t0 + tq;
-        const __nv_bfloat16* qr = proj + m * P.proj_stride + P.q_rot_col0 + (size_t)(h0 + hh) * P.q_head_stride;
-        const float u = __bfloat162float(qr[d]), w = (d + 1 < R) ? __bfloat162float(qr[d + 1]) : 0.f;
-        if (d + 1 < P.rot_dims) {
-          const float* cs = P.rope + (size_t)P.pos_ids[t0 + tq] * P.rot_dims + d;
-          v0 = u * cs[0] - w * cs[1];
-          v1 = w * cs[0] + u * cs[1];
-        } else {
-          v0 = u;
-          v1 = w;
+      const bool live = tq < ntok && hh < HB;
+      const size_t m = (size_t)b * P.Tn + t0 + (live ? tq : 0);
+      const __nv_bfloat16* qr = proj + m * P.proj_stride + P.q_rot_col0 + (size_t)(h0 + (live ? hh : 0)) * P.q_head_stride;
+      const float* cs_row = P.rope + (size_t)(live ? P.pos_ids[t0 + tq] : 0) * P.rot_dims;
+      for (int pi = lane; pi < npair; pi += 32) {
+        const int d = 2 * pi;
+        float v0 = 0.f, v1 = 0.f;
+        if (live && d < R) {
+          const float u = __bfloat162float(qr[d]), w = (d + 1 < R) ? __bfloat162float(qr[d + 1]) : 0.f;
+          if (d + 1 < P.rot_dims) {
+            const float c0 = cs_row[d], s0 = cs_row[d + 1];
+            v0 = u * c0 - w * s0;
+            v1 = w * c0 + u * s0;
+          } else {
+            v0 = u;
+            v1 = w;
+          }
         }
+        if (KR + d < G.DKP) Qs[r * pitch + KR + d] = __float2bfloat16_rn(v0);
+        if (KR + d + 1 < G.DKP) Qs[r * pitch + KR + d + 1] = __float2bfloat16_rn(v1);
       }
-      if (KR + d < G.DKP) Qs[r * pitch + KR + d] = __float2bfloat16_rn(v0);
-      if (KR + d + 1 < G.DKP) Qs[r * pitch + KR + d + 1] = __float2bfloat16_rn(v1);
     }
   }
   // zero the padding columns of the key rows once (the loads below never touch them)
@@ -338,10 +335,14 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
     const int nk = min(LM_KC, j_end - j0);
     if (vec) {
       const int cpr = Dk / 8;
-      for (int ch = tid; ch < LM_KC * cpr; ch += LM_THREADS) {
-        const int jj = ch / cpr, c8 = (ch - jj * cpr) * 8;
+      int slot = (j0 + warp) % P.cache_len;
+      for (int jj = warp; jj < LM_KC; jj += LM_THREADS / 32) {
         const bool ok = jj < nk;
-        la_cp_async16(dst + jj * pitch + c8, cache + (size_t)((ok ? j0 + jj : j0) % P.cache_len) * Dk + c8, ok);
+        const __nv_bfloat16* src = cache + (size_t)(ok ? slot : 0) * Dk;
+        __nv_bfloat16* d = dst + jj * pitch;
+        for (int c = lane; c < cpr; c += 32) la_cp_async16(d + c * 8, src + c * 8, ok);
+        slot += LM_THREADS / 32;
+        while (slot >= P.cache_len) slot -= P.cache_len;
       }
     } else {
       for (int idx = tid; idx < LM_KC * Dk; idx += LM_THREADS) {
@@ -455,22 +456,32 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
 #pragma unroll
   for (int i = 0; i < 2; ++i)
 #pragma unroll
-    for (int j = 0; j < NTW; ++j)
+    for (int hf = 0; hf < 2; ++hf) {           // the rows this thread holds: resolved once, columns walked below
+      const int r = i * 16 + (lane >> 2) + hf * 8;
+      if (row_pos[r] < 0) continue;
+      const int tq = r / G.HB, hh = r - tq * G.HB;
+      const size_t m = (size_t)b * P.Tn + t0 + tq;
+      if (P.splits == 1) {
+        float g = 1.f;
+        if (P.gate_col0 >= 0) g = 1.f / (1.f + expf(-__bfloat162float(proj[m * P.proj_stride + P.gate_col0 + h0 + hh])));
+        const float f = g / l_run[r];
+        __nv_bfloat16* orow = out + (size_t)((h0 + hh) * P.os_h + (long long)m * P.os_m);
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int r = i * 16 + (lane >> 2) + (q >> 1) * 8;
-        const int col = wcol0 + j * 8 + (lane & 3) * 2 + (q & 1);
-        if (row_pos[r] < 0 || col >= KR) continue;
-        const int tq = r / G.HB, hh = r - tq * G.HB;
-        const size_t m = (size_t)b * P.Tn + t0 + tq;
-        if (P.splits == 1) {
-          float g = 1.f;
-          if (P.gate_col0 >= 0) g = 1.f / (1.f + expf(-__bfloat162float(proj[m * P.proj_stride + P.gate_col0 + h0 + hh])));
-          out[(size_t)((h0 + hh) * P.os_h + (long long)m * P.os_m + col)] = __float2bfloat16_rn(acc[i][j][q] / l_run[r] * g);
-        } else {
-          P.scratch[((m * P.H + h0 + hh) * P.splits + sp) * (KR + 2) + col] = acc[i][j][q];
+        for (int j = 0; j < NTW; ++j) {
+          const int col = wcol0 + j * 8 + (lane & 3) * 2;
+          if (col < KR) orow[col] = __float2bfloat16_rn(acc[i][j][hf * 2] * f);
+          if (col + 1 < KR) orow[col + 1] = __float2bfloat16_rn(acc[i][j][hf * 2 + 1] * f);
+        }
+      } else {
+        float* srow = P.scratch + ((m * P.H + h0 + hh) * P.splits + sp) * (KR + 2);
+#pragma unroll
+        for (int j = 0; j < NTW; ++j) {
+          const int col = wcol0 + j * 8 + (lane & 3) * 2;
+          if (col < KR) srow[col] = acc[i][j][hf * 2];
+          if (col + 1 < KR) srow[col + 1] = acc[i][j][hf * 2 + 1];
         }
       }
+    }
   if (P.splits > 1 && tid < LM_ROWS && row_pos[tid] >= 0) {
     const int tq = tid / G.HB, hh = tid - tq * G.HB;
     const size_t m = (size_t)b * P.Tn + t0 + tq;
@@ -514,13 +525,23 @@ __global__ void latent_attn_combine_kernel(const LatentAttnParams P) {
   float g = 1.f;
   if (P.gate_col0 >= 0) g = 1.f / (1.f + expf(-dt<T>::ld((const T*)P.proj + (size_t)m * P.proj_stride, P.gate_col0 + h)));
   T* out = (T*)P.out;
-  for (int i = threadIdx.x; i < KR; i += blockDim.x) {
-    float v = 0.f;
-    for (int s = 0; s < P.splits; ++s) {
-      const float ms = base[s * (KR + 2) + KR];
-      if (ms != -INFINITY) v += expf(ms - mx) * base[s * (KR + 2) + i];
+  __shared__ float wsp[64];                      // weight of every split, with 1 / l and the gate folded in
+  for (int s0 = 0; s0 < P.splits; s0 += 64) {    // 64 splits at a time (in split order)
+    const int ns = min(64, P.splits - s0);
+    __syncthreads();
+    if ((int)threadIdx.x < ns) {
+      const float ms = base[(s0 + threadIdx.x) * (KR + 2) + KR];
+      wsp[threadIdx.x] = (ms != -INFINITY) ? expf(ms - mx) / l * g : 0.f;
     }
-    dt<T>::st(out, (size_t)(h * P.os_h + (long long)m * P.os_m + i), v / l * g);
+    __syncthreads();
+    for (int i = threadIdx.x; i < KR; i += blockDim.x) {
+      float v = 0.f;
+#pragma unroll 8
+      for (int s = 0; s < ns; ++s) v += wsp[s] * base[(size_t)(s0 + s) * (KR + 2) + i];
+      const size_t o = (size_t)(h * P.os_h + (long long)m * P.os_m + i);
+      if (s0 > 0) v += dt<T>::ld(out, o);
+      dt<T>::st(out, o, v);
+    }
   }
 }
 

@@ -24,7 +24,7 @@ namespace llb {
 namespace {
 
 constexpr int MT_BN = 128;                 // rows of one B box
-constexpr int MT_STAGES = 4;
+constexpr int MT_STAGES = 2;                 // two CTAs per SM: one CTA's prologue and epilogue run under the other's main loop
 constexpr int MT_A_BYTES = BM * BK * 2, MT_B_BYTES = 2 * MT_BN * BK * 2;
 constexpr int MT_TMEM_COLS = 256;
 constexpr uint32_t MT_WAIT_LIMIT = 1u << 22;
@@ -47,7 +47,7 @@ __device__ __forceinline__ void tma_box(void* dst, const CUtensorMap* map, int x
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(192, 1) moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(192, 2) moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                              const __grid_constant__ CUtensorMap map_b,
                                                              const int32_t* __restrict__ offsets, const int32_t* __restrict__ perm,
                                                              int X, int N, int K, float limit, float alpha,
@@ -64,21 +64,8 @@ __global__ void __launch_bounds__(192, 1) moe_gemm_tc_kernel(const __grid_consta
   int* s_fail = s_tile + 3;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) {
-    int t = blockIdx.y, found = -1, e = 0;
-    for (; e < X; ++e) {
-      const int cnt = offsets[e + 1] - offsets[e];
-      const int tiles = (cnt + BM - 1) / BM;
-      if (t < tiles) { found = e; break; }
-      t -= tiles;
-    }
-    s_tile[0] = found;
-    if (found >= 0) {
-      s_tile[1] = offsets[found] + t * BM;
-      s_tile[2] = min(BM, offsets[found + 1] - s_tile[1]);
-    }
-    *s_fail = 0;
-  }
+  if (warp == 0) grouped_tile_lookup(offsets, X, blockIdx.y, BM, s_tile);
+  if (threadIdx.x == 32) *s_fail = 0;
   __syncthreads();
   if (s_tile[0] < 0) return;                       // before anything is allocated
   const int e = s_tile[0], r0 = s_tile[1], cnt = s_tile[2];

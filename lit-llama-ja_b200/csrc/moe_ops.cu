@@ -138,25 +138,12 @@ __global__ void __launch_bounds__(GG_THREADS) moe_grouped_gemm_kernel(const T* _
   __shared__ float As[GG_BK][BM + 1];
   __shared__ float Bs[NB][GG_BK][GG_BN + 1];
   __shared__ int32_t src_row[BM], dst_row[BM];
-  __shared__ int s_e, s_r0, s_cnt;
+  __shared__ int s_tile[3];
   const int tid = threadIdx.x;
-  if (tid == 0) {
-    int t = blockIdx.x, e = 0, found = -1;
-    for (; e < X; ++e) {
-      const int cnt = offsets[e + 1] - offsets[e];
-      const int tiles = (cnt + BM - 1) / BM;
-      if (t < tiles) { found = e; break; }
-      t -= tiles;
-    }
-    s_e = found;
-    if (found >= 0) {
-      s_r0 = offsets[found] + t * BM;
-      s_cnt = min(BM, offsets[found + 1] - s_r0);
-    }
-  }
+  if (tid < 32) grouped_tile_lookup(offsets, X, blockIdx.x, BM, s_tile);
   __syncthreads();
-  if (s_e < 0) return;
-  const int e = s_e, r0 = s_r0, cnt = s_cnt;
+  if (s_tile[0] < 0) return;
+  const int e = s_tile[0], r0 = s_tile[1], cnt = s_tile[2];
   const int n0 = blockIdx.y * GG_BN;
   if (tid < BM) {
     const int r = r0 + min(tid, cnt - 1);
@@ -255,25 +242,12 @@ __global__ void __launch_bounds__(GM_THREADS) moe_grouped_gemm_mma_kernel(
   __nv_bfloat16* As = (__nv_bfloat16*)gm_smem;                               // [2][BM][PITCH]
   __nv_bfloat16* Bs = As + 2 * BM * GM_PITCH;                                // [2][NB][BN][PITCH]
   __shared__ int32_t src_row[BM], dst_row[BM];
-  __shared__ int s_e, s_r0, s_cnt;
+  __shared__ int s_tile[3];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) {
-    int t = blockIdx.x, e = 0, found = -1;
-    for (; e < X; ++e) {
-      const int cnt = offsets[e + 1] - offsets[e];
-      const int tiles = (cnt + BM - 1) / BM;
-      if (t < tiles) { found = e; break; }
-      t -= tiles;
-    }
-    s_e = found;
-    if (found >= 0) {
-      s_r0 = offsets[found] + t * BM;
-      s_cnt = min(BM, offsets[found + 1] - s_r0);
-    }
-  }
+  if (warp == 0) grouped_tile_lookup(offsets, X, blockIdx.x, BM, s_tile);
   __syncthreads();
-  if (s_e < 0) return;
-  const int e = s_e, r0 = s_r0, cnt = s_cnt;
+  if (s_tile[0] < 0) return;
+  const int e = s_tile[0], r0 = s_tile[1], cnt = s_tile[2];
   const int n0 = blockIdx.y * GM_BN;
   for (int i = tid; i < BM; i += GM_THREADS) {
     const int r = r0 + min(i, cnt - 1);

@@ -216,8 +216,11 @@ __global__ void __launch_bounds__(GG_THREADS) moe_grouped_gemm_kernel(const T* _
 
 // ---- bf16 tensor-core form of the same grouped GEMM (mma.sync m16n8k16, fp32 accumulation) ----
 // 128 threads; a block = BM sorted rows of one expert x 64 output columns (x2 matrices for the GLU), K in steps of 64
-// through a two-stage cp.async ring.  Needs 16-byte aligned rows (K, lda multiples of 8); other shapes take the kernel above.
+// through a cp.async ring (two stages, four for the 16-row tiles of decoding).  Needs 16-byte aligned rows (K, lda multiples of 8); other shapes take the kernel above.
 constexpr int GM_BN = 64, GM_BK = 64, GM_PITCH = GM_BK + 8, GM_THREADS = 128;
+// stages of the operand ring: narrow row tiles (decoding: a few rows per expert, the weights are the traffic) keep more
+// k-steps in flight per block
+__host__ __device__ constexpr int gm_stages(int bm) { return bm <= 16 ? 4 : 2; }
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
   const int n = valid ? 16 : 0;
@@ -236,11 +239,12 @@ __global__ void __launch_bounds__(GM_THREADS) moe_grouped_gemm_mma_kernel(
     const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, const int32_t* __restrict__ offsets,
     const int32_t* __restrict__ perm, int top, int X, int N, int K, float limit, float alpha, __nv_bfloat16* __restrict__ c, int ldc) {
   constexpr int NB = MODE == MODE_GLU ? 2 : 1;
+  constexpr int ST = gm_stages(BM);
   constexpr int WARPS_M = BM >= 32 ? 2 : 1, WARPS_N = 4 / WARPS_M;
   constexpr int WM = BM / WARPS_M, WN = GM_BN / WARPS_N, MT = WM / 16, NT = WN / 8;
   extern __shared__ __align__(16) unsigned char gm_smem[];
-  __nv_bfloat16* As = (__nv_bfloat16*)gm_smem;                               // [2][BM][PITCH]
-  __nv_bfloat16* Bs = As + 2 * BM * GM_PITCH;                                // [2][NB][BN][PITCH]
+  __nv_bfloat16* As = (__nv_bfloat16*)gm_smem;                               // [ST][BM][PITCH]
+  __nv_bfloat16* Bs = As + ST * BM * GM_PITCH;                               // [ST][NB][BN][PITCH]
   __shared__ int32_t src_row[BM], dst_row[BM];
   __shared__ int s_tile[3];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -286,12 +290,18 @@ __global__ void __launch_bounds__(GM_THREADS) moe_grouped_gemm_mma_kernel(
         for (int q = 0; q < 4; ++q) acc[b][i][j][q] = 0.f;
   const int wm0 = (warp / WARPS_N) * WM, wn0 = (warp % WARPS_N) * WN;
   const int nk = (K + GM_BK - 1) / GM_BK;
-  load_stage(0, 0);
+  // a ring of ST stages: ST - 1 k-steps are in flight under the math of one (a group is committed every step, empty
+  // past the end, so that "all but the newest ST - 1 groups" always means "this step's operands have landed")
+#pragma unroll
+  for (int s = 0; s < ST - 1; ++s) {
+    if (s < nk) load_stage(s, s * GM_BK); else cp_async_commit();
+  }
   for (int kt = 0; kt < nk; ++kt) {
-    if (kt + 1 < nk) { load_stage((kt + 1) & 1, (kt + 1) * GM_BK); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    if (kt + ST - 1 < nk) load_stage((kt + ST - 1) % ST, (kt + ST - 1) * GM_BK); else cp_async_commit();
+    cp_async_wait<ST - 1>();
     __syncthreads();
-    const __nv_bfloat16* as = As + (kt & 1) * BM * GM_PITCH;
-    const __nv_bfloat16* bs = Bs + (kt & 1) * NB * GM_BN * GM_PITCH;
+    const __nv_bfloat16* as = As + (kt % ST) * BM * GM_PITCH;
+    const __nv_bfloat16* bs = Bs + (kt % ST) * NB * GM_BN * GM_PITCH;
 #pragma unroll
     for (int ks = 0; ks < GM_BK / 16; ++ks) {
       uint32_t af[MT][4];
@@ -337,7 +347,7 @@ template <int BM, int MODE>
 static int launch_grouped_mma(const void* a, int lda, const void* w, const int32_t* offsets, const int32_t* perm, int top, int X, int N,
                               int K, float limit, float alpha, void* c, int ldc, int n_rows, cudaStream_t st) {
   constexpr int NB = MODE == MODE_GLU ? 2 : 1;
-  const size_t smem = sizeof(__nv_bfloat16) * 2 * (BM + NB * GM_BN) * GM_PITCH;
+  const size_t smem = sizeof(__nv_bfloat16) * gm_stages(BM) * (BM + NB * GM_BN) * GM_PITCH;
   static bool once = false;
   if (!once) {
     LL_CUDA(cudaFuncSetAttribute(moe_grouped_gemm_mma_kernel<BM, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -208,9 +208,11 @@ __global__ void __launch_bounds__(LA_THREADS) latent_attn_kernel(const LatentAtt
 
 // ---- bf16 tensor-core form (mma.sync m16n8k16, fp32 scores / softmax / accumulation) ----
 // A block owns 32 query rows = (a few consecutive tokens) x (up to 32 heads) and walks the union of their windows in
-// chunks of 64 cache rows: S = Q K^T (all heads against the same rows), online softmax in fp32, O += P C with the
-// accumulators of the 32 x kv_rank output split by columns over the 8 warps (NTW n-tiles of 8 columns each).
-constexpr int LM_ROWS = 32, LM_KC = 64, LM_THREADS = 256;
+// chunks of 64 cache rows: S = Q K^T (all heads against the same rows; a warp takes 16 rows x 16 keys x half of the row's
+// dimensions, the two halves meet in shared memory), online softmax in fp32, O += P C with the accumulators of the
+// 32 x kv_rank output split by columns over the 16 warps (NTW n-tiles of 8 columns each).  Sixteen warps, four per
+// scheduler: every phase is a chain of shared-memory loads and tensor instructions whose latency the other warps cover.
+constexpr int LM_ROWS = 32, LM_KC = 64, LM_THREADS = 512, LM_WARPS = LM_THREADS / 32;
 
 __device__ __forceinline__ void la_cp_async16(void* smem, const void* gmem, bool valid) {
   const int n = valid ? 16 : 0;
@@ -240,8 +242,8 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
   __nv_bfloat16* Qs = (__nv_bfloat16*)la_smem;                 // [32][pitch]
   __nv_bfloat16* Ks0 = Qs + LM_ROWS * pitch;                   // [2 stages][64][pitch]
   __nv_bfloat16* Ps = Ks0 + 2 * LM_KC * pitch;                 // [32][64 + 8]
-  float* Ss = (float*)(Ps + LM_ROWS * (LM_KC + 8));            // [32][64 + 1]
-  float* m_run = Ss + LM_ROWS * (LM_KC + 1);                   // [32]
+  float* Ss = (float*)(Ps + LM_ROWS * (LM_KC + 8));            // [2 halves of the row's dimensions][32][64 + 1]
+  float* m_run = Ss + 2 * LM_ROWS * (LM_KC + 1);               // [32]
   float* l_run = m_run + LM_ROWS;
   float* corr = l_run + LM_ROWS;
   int* row_pos = (int*)(corr + LM_ROWS);                       // [32] position of the row's token, -1: padding row
@@ -361,8 +363,8 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();            // this chunk has landed; every warp is done with the other stage, with Ss and with Ps
     if (j0 + LM_KC < j_end) load_keys(stage ^ 1, j0 + LM_KC);     // the next chunk travels under this chunk's math
-    {   // S = Q K^T: warp -> m-tile (warp & 1), key columns (warp >> 1) * 16 .. + 15
-      const int mt = warp & 1, np = warp >> 1;
+    {   // S = Q K^T: warp -> m-tile (warp & 1), key columns ((warp >> 1) & 3) * 16 .. + 15, half (warp >> 3) of the k-steps
+      const int mt = warp & 1, np = (warp >> 1) & 3, kh = warp >> 3;
       float part[4][2][4];     // four interleaved slices of the k range: independent accumulation chains, summed below
 #pragma unroll
       for (int c = 0; c < 4; ++c)
@@ -370,8 +372,9 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
         for (int j = 0; j < 2; ++j)
 #pragma unroll
           for (int q = 0; q < 4; ++q) part[c][j][q] = 0.f;
-      const int nks = G.DKP / 16;
-      for (int ks0 = 0; ks0 < nks; ks0 += 4) {
+      const int nks_all = G.DKP / 16, nks_half = (nks_all + 1) / 2;
+      const int ks_begin = kh * nks_half, nks = min(nks_all, ks_begin + nks_half);
+      for (int ks0 = ks_begin; ks0 < nks; ks0 += 4) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int ks = ks0 + c;
@@ -397,12 +400,13 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
           const int col = np * 16 + j * 8 + (lane & 3) * 2 + (q & 1);
           const int pr = row_pos[r], jpos = j0 + col;
           const bool vis = pr >= 0 && col < nk && jpos <= pr && (P.window <= 0 || jpos > pr - P.window);
-          Ss[r * (LM_KC + 1) + col] = vis ? sacc[j][q] * P.scale : -INFINITY;
+          Ss[(kh * LM_ROWS + r) * (LM_KC + 1) + col] = vis ? sacc[j][q] * P.scale : -INFINITY;
         }
     }
     __syncthreads();
-    for (int r = warp * 4; r < warp * 4 + 4; ++r) {   // online softmax: 4 rows per warp, 2 columns per lane
-      const float s0 = Ss[r * (LM_KC + 1) + lane], s1 = Ss[r * (LM_KC + 1) + lane + 32];
+    for (int r = warp * (LM_ROWS / LM_WARPS); r < (warp + 1) * (LM_ROWS / LM_WARPS); ++r) {   // online softmax: 2 columns per lane
+      const float* sb = Ss + (LM_ROWS + r) * (LM_KC + 1);     // the other half of the dimensions (-inf + -inf stays -inf)
+      const float s0 = Ss[r * (LM_KC + 1) + lane] + sb[lane], s1 = Ss[r * (LM_KC + 1) + lane + 32] + sb[lane + 32];
       const float mo = m_run[r];
       const float mn = fmaxf(mo, warp_max(fmaxf(s0, s1)));
       const float p0 = (s0 == -INFINITY) ? 0.f : expf(s0 - mn), p1 = (s1 == -INFINITY) ? 0.f : expf(s1 - mn);
@@ -493,7 +497,7 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
 
 static size_t latent_mma_smem(int pitch) {
   return sizeof(__nv_bfloat16) * ((size_t)(LM_ROWS + 2 * LM_KC) * pitch + (size_t)LM_ROWS * (LM_KC + 8)) +
-         sizeof(float) * ((size_t)LM_ROWS * (LM_KC + 1) + 3 * LM_ROWS) + sizeof(int) * LM_ROWS;
+         sizeof(float) * ((size_t)2 * LM_ROWS * (LM_KC + 1) + 3 * LM_ROWS) + sizeof(int) * LM_ROWS;
 }
 
 template <int NTW>
@@ -629,12 +633,11 @@ int ll_latent_attn(const void* q_lat, long long qs_h, long long qs_m, const void
     G.DKP = (Dk + 15) / 16 * 16;
     G.pitch = G.DKP + 8;
     if (latent_mma_smem(G.pitch) <= 220 * 1024) {
-      const int cols_per_warp = (kv_rank + 7) / 8;
+      const int cols_per_warp = (kv_rank + LM_WARPS - 1) / LM_WARPS;
       int rc;
       if (cols_per_warp <= 8) rc = launch_latent_mma<1>(P, G, B, st);
       else if (cols_per_warp <= 16) rc = launch_latent_mma<2>(P, G, B, st);
-      else if (cols_per_warp <= 32) rc = launch_latent_mma<4>(P, G, B, st);
-      else rc = launch_latent_mma<8>(P, G, B, st);
+      else rc = launch_latent_mma<4>(P, G, B, st);
       if (rc != LL_OK) return rc;
       done = true;
     }

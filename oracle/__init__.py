@@ -3,7 +3,7 @@
 TEST INFRASTRUCTURE ONLY.  Nothing under ``oracle/`` is imported by the product
 package (``lit-llama-ja_b200/``); only ``tests/``, ``__graft_entry__.smoke()`` and
 ``bench.py``'s ``cpu_baseline`` / ``--impl reference`` legs may use it, and there
-only as the checker / the timed CPU baseline.
+only as the thing results are compared with / the timed CPU baseline.
 
 It is a plain-numpy restatement of the reference's algorithms (every function
 cites the reference file:line it follows).  Parity status:

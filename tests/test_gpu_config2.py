@@ -235,7 +235,7 @@ def test_gptq_int8_fused_decode_chain_at_7b_shapes_vs_oracle_and_module_path():
 @pytest.mark.parametrize("group", [128])
 def test_fused_decode_chain_vs_the_reference_modules_on_the_gpu(g128, group):
     """(c): the unmodified reference's LLaMA + ColBlockQuantizedLinear (group 128 -> get_weight + F.linear on CUDA) loaded
-    from OUR state dict (strict: the checkpoint layout is the contract), same tokens, teacher-forced."""
+    from OUR state dict (strict: the checkpoint layout is fixed), same tokens, teacher-forced."""
     from baseline import ref_loader
 
     if not ref_loader.available():

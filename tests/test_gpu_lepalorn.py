@@ -176,3 +176,34 @@ def test_trace_session_replays_steps(mixed):
     assert rel_err(got, want[3:4]) < TOL[torch.float32]
     with pytest.raises(RuntimeError):
         s.step([{"id": "c", "tokens": [1], "want": []}])
+
+
+def test_long_prompt_takes_the_tensor_core_expert_path(tmp_path, monkeypatch):
+    """A prompt with hundreds of (token, choice) rows per step: with the thresholds lowered the expert GEMMs of the
+    prefill run on the tcgen05 kernels inside the model (also in portions, whose row counts differ), and decoding after
+    it on the small-step kernels; both against the oracle, and the prefill against the same model kept off that path."""
+    import lit_llama.moe as MOE
+    from lit_llama import _native as N
+
+    layers = [
+        (O.mixer_cfg(4, 16, 8, 16, 24, 33, base=1000.0), O.mlp_cfg(6, 2, 40, 0.8, 24, 1.2)),
+        (O.mixer_cfg(2, 8, 8, 24, 24, 150, base=1000.0, kv_from=0), O.mlp_cfg(3, 3, 72, 1.0)),
+    ]
+    cfg = O.model_cfg(83, 64, layers, eps=1e-5, embedding_scale=2.0)
+    W = O.random_weights(cfg, 21)
+    folder = write_model(tmp_path / "wide", cfg, W)
+    toks = np.random.RandomState(22).randint(0, cfg["vocab"], size=260).tolist()
+    want = O.forward(cfg, W, toks)
+    m = load(folder, torch.bfloat16)
+    monkeypatch.setattr(MOE, "TC_MIN_ROWS", 1 << 30)
+    plain = run_schedule(m, toks, [len(toks)], 300)[0]
+    monkeypatch.setattr(MOE, "TC_MIN_ROWS", 128)
+    monkeypatch.setattr(MOE, "TC_MIN_ROWS_PER_EXPERT", 1)
+    x = torch.zeros((250, 64), dtype=torch.bfloat16, device="cuda")
+    assert all(b.mlp.takes_tensor_cores(250 * b.mlp.spec.top, x) for b in m.blocks)
+    got = run_schedule(m, toks, [250] + [1] * 10, 300)[0]
+    assert N.call_ret("ll_moe_tc_error") == 0
+    assert agrees(got, want, torch.bfloat16), (rel_err(got, want), rms_err(got, want))
+    assert rms_err(got, plain) < RMS_TOL[torch.bfloat16]
+    got = run_schedule(m, toks, [130, 70, 60], 300)[0]
+    assert agrees(got, want, torch.bfloat16), (rel_err(got, want), rms_err(got, want))

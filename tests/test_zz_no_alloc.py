@@ -1,6 +1,6 @@
 """ll_int4_gemm_tc_static (include/llb200.h): the fused int4 de-quantise + GEMM with its split-K scratch in an array built
 into the library, for callers that cannot call cudaMalloc.  No counterpart in the reference (added at the request of the
-run's operators); the checker is the existing entry point ll_int4_gemm_tc on the same inputs, whose own parity against the
+run's operators); it is compared with the existing entry point ll_int4_gemm_tc on the same inputs, whose own parity against the
 oracle is tests/test_gpu_quant.py::test_int4_fused_dequant_gemm_vs_oracle.
 
 This file is named to be collected LAST: the round's end runs `pytest -x`, so a failure here hides nothing after it.

@@ -13,7 +13,8 @@
 //   down: columns 0..255 = 256 outputs, scattered to (token, choice) order by the epilogue.
 // A row tile may run past its expert's last row: those rows (the next expert's, or zero fill) are
 // computed and never stored.
-//   warp 0   : TMA producer (A box 128 x 64, two B boxes 128 x 64, 128-byte swizzle) into a 4-stage ring
+//   warp 0   : TMA producer (A box 128 x 64, two B boxes 128 x 64, 128-byte swizzle) into a 2-stage ring; two CTAs
+//              share an SM (2 x 256 TMEM columns), so one CTA's first loads and epilogue run under the other's MMAs
 //   warp 1   : TMEM allocation, one thread issues tcgen05.mma 128 x 256 x 16 (bf16 in, fp32 accumulate)
 //   warps 2-5: epilogue, one accumulator row per thread
 // Every wait on an mbarrier is bounded; a wait that runs out records a code in g_moe_tc_error, the roles

@@ -215,10 +215,11 @@ def test_router_permutation_and_grouped_experts(dtype, shape):
     close(host(moe(dev(h, dtype))), O.moe(h, {k: np.asarray(v, dtype=np.float64) for k, v in W.items()}, "l0.mlp.", cfgf), TOL[dtype] * 3)
 
 
-@pytest.mark.parametrize("shape", [(1500, 64, 5, 2, 72), (700, 320, 3, 3, 40), (1100, 200, 7, 2, 136), (2300, 512, 4, 1, 264)])
+@pytest.mark.parametrize("shape", [(1500, 64, 5, 2, 72), (700, 320, 3, 3, 40), (1100, 200, 7, 2, 136), (2300, 512, 4, 1, 264), (1900, 64, 40, 2, 24)])
 def test_grouped_experts_on_the_tcgen05_path(shape, monkeypatch):
     """Many rows per expert: the tensor-core kernels (row tiles of 128 that run past an expert's last row, an output
-    width that is no multiple of the tile, a K that is no multiple of 64, an empty expert) against the float64 oracle
+    width that is no multiple of the tile, a K that is no multiple of 64, an empty expert, more experts than one pass of
+    the tile lookup examines) against the float64 oracle
     and against the kernels that small steps take."""
     import lit_llama.moe as MOE
     from lit_llama import _native as N

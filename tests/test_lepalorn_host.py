@@ -177,3 +177,22 @@ def test_trace_session_bookkeeping():
         s.step([{"id": "b", "tokens": list(range(10)), "want": []}])
     with pytest.raises(RuntimeError, match="still hold"):
         s.step([{"id": "c", "tokens": [1], "want": []}])
+
+
+def test_expert_gemm_path_choice():
+    """Which steps run their expert GEMMs on the tcgen05 kernels: bfloat16, rows TMA can tile, enough rows per expert."""
+    from lit_llama.moe import MoE, MoESpec, TC_MIN_ROWS, TC_MIN_ROWS_PER_EXPERT
+
+    moe = MoE(MoESpec(64, 4, 2, 24, 1.0), torch.bfloat16, "cpu")
+    x = torch.zeros((TC_MIN_ROWS, 64), dtype=torch.bfloat16)
+    n = max(TC_MIN_ROWS, TC_MIN_ROWS_PER_EXPERT * 4)
+    assert moe.takes_tensor_cores(n, x)
+    assert not moe.takes_tensor_cores(TC_MIN_ROWS - 1, x)                      # a small step
+    assert not moe.takes_tensor_cores(n, x.float())                            # float32 stays on the fp32 kernels
+    assert not moe.takes_tensor_cores(n, torch.zeros((8, 72), dtype=torch.bfloat16)[:, :64][:, ::1].as_strided((8, 64), (68, 1)))
+    many = MoE(MoESpec(64, 64, 2, 24, 1.0), torch.bfloat16, "cpu")
+    assert not many.takes_tensor_cores(TC_MIN_ROWS_PER_EXPERT * 64 - 1, x)     # too few rows per expert for 128-row tiles
+    odd = MoE(MoESpec(60, 4, 2, 24, 1.0), torch.bfloat16, "cpu")
+    assert not odd.takes_tensor_cores(n, torch.zeros((8, 60), dtype=torch.bfloat16))   # rows that are no 16-byte multiple
+    odd_ff = MoE(MoESpec(64, 4, 2, 20, 1.0), torch.bfloat16, "cpu")
+    assert not odd_ff.takes_tensor_cores(n, x)

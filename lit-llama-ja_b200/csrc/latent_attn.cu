@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(LA_THREADS) latent_attn_kernel(const LatentAtt
 // dimensions, the two halves meet in shared memory), online softmax in fp32, O += P C with the accumulators of the
 // 32 x kv_rank output split by columns over the 16 warps (NTW n-tiles of 8 columns each).  Sixteen warps, four per
 // scheduler: every phase is a chain of shared-memory loads and tensor instructions whose latency the other warps cover.
-constexpr int LM_ROWS = 32, LM_KC = 64, LM_THREADS = 512, LM_WARPS = LM_THREADS / 32;
+constexpr int LM_ROWS = 32, LM_KC = 64;
 
 __device__ __forceinline__ void la_cp_async16(void* smem, const void* gmem, bool valid) {
   const int n = valid ? 16 : 0;
@@ -234,8 +234,11 @@ struct LatentMmaGeom {
   int HB, TQ, DKP, pitch;   // heads and tokens per block (HB * TQ <= 32), padded row length, shared-memory row pitch (elements)
 };
 
-template <int NTW>
-__global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const LatentAttnParams P, const LatentMmaGeom G) {
+// WARPS = 16: one block per SM, four warps per scheduler, the score product split over halves of the dimensions.
+// WARPS = 8: for rows short enough that two blocks share an SM (the same number of warps, two chunks in different phases).
+template <int NTW, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) latent_attn_mma_kernel(const LatentAttnParams P, const LatentMmaGeom G) {
+  constexpr int LM_THREADS = WARPS * 32, LM_WARPS = WARPS;
   extern __shared__ __align__(16) unsigned char la_smem[];
   const int KR = P.kv_rank, R = P.rot_dim, Dk = KR + R;
   const int pitch = G.pitch;
@@ -243,7 +246,7 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
   __nv_bfloat16* Ks0 = Qs + LM_ROWS * pitch;                   // [2 stages][64][pitch]
   __nv_bfloat16* Ps = Ks0 + 2 * LM_KC * pitch;                 // [32][64 + 8]
   float* Ss = (float*)(Ps + LM_ROWS * (LM_KC + 8));            // [2 halves of the row's dimensions][32][64 + 1]
-  float* m_run = Ss + 2 * LM_ROWS * (LM_KC + 1);               // [32]
+  float* m_run = Ss + (WARPS == 16 ? 2 : 1) * LM_ROWS * (LM_KC + 1);   // [32]
   float* l_run = m_run + LM_ROWS;
   float* corr = l_run + LM_ROWS;
   int* row_pos = (int*)(corr + LM_ROWS);                       // [32] position of the row's token, -1: padding row
@@ -364,7 +367,7 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
     __syncthreads();            // this chunk has landed; every warp is done with the other stage, with Ss and with Ps
     if (j0 + LM_KC < j_end) load_keys(stage ^ 1, j0 + LM_KC);     // the next chunk travels under this chunk's math
     {   // S = Q K^T: warp -> m-tile (warp & 1), key columns ((warp >> 1) & 3) * 16 .. + 15, half (warp >> 3) of the k-steps
-      const int mt = warp & 1, np = (warp >> 1) & 3, kh = warp >> 3;
+      const int mt = warp & 1, np = (warp >> 1) & 3, kh = WARPS == 16 ? warp >> 3 : 0;
       float part[4][2][4];     // four interleaved slices of the k range: independent accumulation chains, summed below
 #pragma unroll
       for (int c = 0; c < 4; ++c)
@@ -372,7 +375,7 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
         for (int j = 0; j < 2; ++j)
 #pragma unroll
           for (int q = 0; q < 4; ++q) part[c][j][q] = 0.f;
-      const int nks_all = G.DKP / 16, nks_half = (nks_all + 1) / 2;
+      const int nks_all = G.DKP / 16, nks_half = WARPS == 16 ? (nks_all + 1) / 2 : nks_all;
       const int ks_begin = kh * nks_half, nks = min(nks_all, ks_begin + nks_half);
       for (int ks0 = ks_begin; ks0 < nks; ks0 += 4) {
 #pragma unroll
@@ -406,7 +409,8 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
     __syncthreads();
     for (int r = warp * (LM_ROWS / LM_WARPS); r < (warp + 1) * (LM_ROWS / LM_WARPS); ++r) {   // online softmax: 2 columns per lane
       const float* sb = Ss + (LM_ROWS + r) * (LM_KC + 1);     // the other half of the dimensions (-inf + -inf stays -inf)
-      const float s0 = Ss[r * (LM_KC + 1) + lane] + sb[lane], s1 = Ss[r * (LM_KC + 1) + lane + 32] + sb[lane + 32];
+      const float s0 = Ss[r * (LM_KC + 1) + lane] + (WARPS == 16 ? sb[lane] : 0.f);
+      const float s1 = Ss[r * (LM_KC + 1) + lane + 32] + (WARPS == 16 ? sb[lane + 32] : 0.f);
       const float mo = m_run[r];
       const float mn = fmaxf(mo, warp_max(fmaxf(s0, s1)));
       const float p0 = (s0 == -INFINITY) ? 0.f : expf(s0 - mn), p1 = (s1 == -INFINITY) ? 0.f : expf(s1 - mn);
@@ -495,21 +499,21 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attn_mma_kernel(const Laten
   }
 }
 
-static size_t latent_mma_smem(int pitch) {
+static size_t latent_mma_smem(int pitch, int halves) {
   return sizeof(__nv_bfloat16) * ((size_t)(LM_ROWS + 2 * LM_KC) * pitch + (size_t)LM_ROWS * (LM_KC + 8)) +
-         sizeof(float) * ((size_t)2 * LM_ROWS * (LM_KC + 1) + 3 * LM_ROWS) + sizeof(int) * LM_ROWS;
+         sizeof(float) * ((size_t)halves * LM_ROWS * (LM_KC + 1) + 3 * LM_ROWS) + sizeof(int) * LM_ROWS;
 }
 
-template <int NTW>
+template <int NTW, int WARPS>
 static int launch_latent_mma(const LatentAttnParams& P, const LatentMmaGeom& G, int B, cudaStream_t st) {
-  const size_t smem = latent_mma_smem(G.pitch);
+  const size_t smem = latent_mma_smem(G.pitch, WARPS == 16 ? 2 : 1);
   static size_t configured = 0;
   if (smem > configured) {
-    LL_CUDA(cudaFuncSetAttribute(latent_attn_mma_kernel<NTW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LL_CUDA(cudaFuncSetAttribute(latent_attn_mma_kernel<NTW, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
   dim3 grid(B * ((P.Tn + G.TQ - 1) / G.TQ), (P.H + G.HB - 1) / G.HB, P.splits);
-  latent_attn_mma_kernel<NTW><<<grid, LM_THREADS, smem, st>>>(P, G);
+  latent_attn_mma_kernel<NTW, WARPS><<<grid, WARPS * 32, smem, st>>>(P, G);
   LL_LAUNCH_OK("latent_attn_mma_kernel");
   return LL_OK;
 }
@@ -632,12 +636,21 @@ int ll_latent_attn(const void* q_lat, long long qs_h, long long qs_m, const void
     if (G.TQ < 1) G.TQ = 1;
     G.DKP = (Dk + 15) / 16 * 16;
     G.pitch = G.DKP + 8;
-    if (latent_mma_smem(G.pitch) <= 220 * 1024) {
-      const int cols_per_warp = (kv_rank + LM_WARPS - 1) / LM_WARPS;
+    if (latent_mma_smem(G.pitch, 2) <= 220 * 1024) {
+      // two 8-warp blocks per SM when two fit (shared memory, and 32 columns of O per warp at most), else one of 16 warps
+      const bool pair = 2 * (latent_mma_smem(G.pitch, 1) + 1024) <= 227 * 1024 && kv_rank <= 256;
+      const int warps = pair ? 8 : 16;
+      const int cols_per_warp = (kv_rank + warps - 1) / warps;
       int rc;
-      if (cols_per_warp <= 8) rc = launch_latent_mma<1>(P, G, B, st);
-      else if (cols_per_warp <= 16) rc = launch_latent_mma<2>(P, G, B, st);
-      else rc = launch_latent_mma<4>(P, G, B, st);
+      if (pair) {
+        if (cols_per_warp <= 8) rc = launch_latent_mma<1, 8>(P, G, B, st);
+        else if (cols_per_warp <= 16) rc = launch_latent_mma<2, 8>(P, G, B, st);
+        else rc = launch_latent_mma<4, 8>(P, G, B, st);
+      } else {
+        if (cols_per_warp <= 8) rc = launch_latent_mma<1, 16>(P, G, B, st);
+        else if (cols_per_warp <= 16) rc = launch_latent_mma<2, 16>(P, G, B, st);
+        else rc = launch_latent_mma<4, 16>(P, G, B, st);
+      }
       if (rc != LL_OK) return rc;
       done = true;
     }

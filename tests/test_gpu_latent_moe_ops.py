@@ -140,11 +140,14 @@ def _attend_oracle(q_lat, q_rot, gate, rows, pos, window, scale, dims, base, KR)
 
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("splits", [1, 3])
-def test_window_edges_with_a_key_that_dominates(dtype, splits):
+@pytest.mark.parametrize("sizes", [(3, 24, 6), (5, 320, 16)])
+def test_window_edges_with_a_key_that_dominates(dtype, splits, sizes):
     """Position 100 holds a key whose score dwarfs all others.  With a window of 37, the queries at 100 .. 136 must
-    return (almost exactly) its row and the query at 137 must not see it; likewise in the first tokens of a sequence."""
+    return (almost exactly) its row and the query at 137 must not see it; likewise in the first tokens of a sequence.
+    Short rows and rows of hundreds of values (in bfloat16 these take the two block shapes of the tensor-core kernel)."""
     r = np.random.RandomState(3)
-    H, KR, R, dims, base, window, scale = 3, 24, 6, 6, 100.0, 37, 0.5
+    H, KR, R = sizes
+    dims, base, window, scale = R, 100.0, 37, 0.5
     S = 80                                                     # the ring has wrapped by position 137: slot of p is p % 80
     rows = {j: O.bf16_round(0.3 * r.randn(KR + R)).astype(np.float64) for j in range(138 - S, 138)}
     probe = np.zeros(KR)

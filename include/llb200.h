@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define LL_ABI_VERSION 12
+#define LL_ABI_VERSION 13
 
 #define LL_OK 0
 #define LL_ERR_ARG (-1)         /* bad shape / dtype / null pointer */
@@ -410,10 +410,17 @@ LL_API size_t ll_latent_attn_scratch_bytes(int M, int n_head, int kv_rank, int s
 LL_API int ll_moe_route(const void* x, int dtype, const float* w_router, const float* bias, int M, int dim, int n_experts,
                         int top, int32_t* expert_idx, float* expert_w, int32_t* counts, int32_t* rank, int32_t* offsets,
                         int32_t* perm, ll_stream stream);
+/* The same with the scoring as a parameter.  score_all 0: as above.  score_all 1: scores = softmax over ALL experts,
+ * expert_w = chosen scores / (their sum + 1e-20).  n_groups > 1: the experts form n_groups equal groups of neighbours, a
+ * group's score is its largest, and only experts of the keep_groups best groups (ties: lowest index) can be chosen. */
+LL_API int ll_moe_route_scored(const void* x, int dtype, const float* w_router, const float* bias, int M, int dim, int n_experts,
+                               int top, int score_all, int n_groups, int keep_groups, int32_t* expert_idx, float* expert_w,
+                               int32_t* counts, int32_t* rank, int32_t* offsets, int32_t* perm, ll_stream stream);
 
 /* Grouped GEMM over the sorted rows, one expert's weight per row segment; w is the experts' stack.
  * mode 1: w [X][2N][K] = [gate; up]; a [M][lda] read at token perm[r] / top;
  *         c[r][:] = glu(a . gate^T, a . up^T) with ll_glu_clamp's formula, rows in sorted order.
+ * mode 2: as mode 1 with the up branch entering as it is: g * sigmoid(alpha g) * u (limit +inf: no clamp; alpha 1: silu).
  * mode 0: w [X][N][K]; a [n_rows][lda] in sorted order; c[perm[r]][:] = a[r] . w[e]^T. */
 LL_API int ll_moe_grouped_gemm(const void* a, int lda, const void* w, const int32_t* offsets, const int32_t* perm, int mode,
                                int dtype, int n_rows, int top, int n_experts, int N, int K, float limit, float alpha,
@@ -433,6 +440,68 @@ LL_API int ll_moe_tc_error(void);
  * given; shared_gate NULL: the shared expert is added as it is). */
 LL_API int ll_moe_combine(const void* y, const float* expert_w, int top, const void* shared_y, int shared_ld,
                           const void* shared_gate, int gate_ld, void* out, int dtype, int M, int dim, ll_stream stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Two-branch layers on an fp32 stream (csrc/residual_ops.cu)
+ * ------------------------------------------------------------------------------------- */
+
+/* x[m][:] += s0 * a0 + s1 * a1 + s2 * a2 (each optional, activation dtype), in place; then with n = x / sqrt(mean(x^2) + eps):
+ * out1 = n * w1 (fp32 when out1_f32, else the activation dtype; optional), out2 = n * w2 (activation dtype; optional). */
+LL_API int ll_add_norm_pair(float* x, const void* a0, float s0, const void* a1, float s1, const void* a2, float s2, const float* w1,
+                            const float* w2, float eps, void* out1, int out1_f32, void* out2, int act_dtype, int rows, int dim,
+                            ll_stream stream);
+/* RMS norm of fp32 rows y [rows][C] in `groups` equal parts with a silu gate (activation dtype, row stride gate_stride):
+ * gate_first 1: (y * silu(g)) / rms_part(.) * w;  0: y / rms_part(y) * w * silu(g).  w: C entries, or C / groups shared by the
+ * parts (w_shared). */
+LL_API int ll_gated_group_norm(const float* y, const void* gate, int gate_stride, const float* w, int w_shared, float eps, int groups,
+                               int gate_first, void* out, int act_dtype, int rows, int C, ll_stream stream);
+/* h <- relu(h)^2, in place */
+LL_API int ll_relu_squared(void* h, int dtype, size_t n, ll_stream stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Short causal convolution with state (csrc/short_conv.cu)
+ * ------------------------------------------------------------------------------------- */
+
+/* y[b][t][c] = (flags & 1 ? x[b][t][c] : 0) + bias[c] + sum_j w[c][j] x[b][t - (taps-1) + j][c], then silu when flags & 2.
+ * x: column slice (col0, C columns) of rows of x_stride elements; w fp32 [C][taps] (last column: the current token); bias
+ * fp32 [C] or NULL; state fp32 [B][taps-1][C]: the last taps-1 inputs, read (unless pos_ids[0] == 0: no past) and replaced. */
+LL_API int ll_short_conv(const void* x, int x_dtype, int x_stride, int col0, const float* w, const float* bias, float* state,
+                         const int32_t* pos_ids, void* y, int y_dtype, int y_stride, int B, int T, int C, int taps, int flags,
+                         ll_stream stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Linear recurrence with diagonal decay (csrc/decay_scan.cu): state-space layers, gated linear attention
+ * ------------------------------------------------------------------------------------- */
+
+/* Per (b, h): S_t[i][c] = a_t[i] S_(t-1)[i][c] + ks_t k_t[i] v_t[c];  y_t[c] = qs sum_i q_t[i] S_t[i][c] + skip[h] v_t[c].
+ * q, k: [B*T][stride], head g = h / (H / qk_heads) at columns g*n..; v: head h at columns h*p..; a: fp32 [B*T][H][n]
+ * (a_per_channel) or [B*T][H]; ks fp32 [B*T][H] or NULL; skip fp32 [H] or NULL; state fp32 [B][H][n][p] (read unless
+ * pos_ids[0] == 0, replaced); y fp32 [B*T][H*p]. */
+LL_API int ll_decay_scan(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, int dtype,
+                         const float* a, int a_per_channel, const float* ks, const float* skip, float qs, float* state,
+                         const int32_t* pos_ids, float* y, int B, int T, int H, int qk_heads, int n, int p, ll_stream stream);
+/* dt = softplus(raw[m][h] + dt_bias[h]); decay = exp(-exp(a_log[h]) dt)   (fp32 [M][H] each) */
+LL_API int ll_ssm_gates(const void* raw, int dtype, int stride, const float* dt_bias, const float* a_log, float* dt_out,
+                        float* decay, int M, int H, ll_stream stream);
+/* out[m][c] = sigmoid(z[m][c] + bias[c])^(1/tau)   (fp32 [M][C]) */
+LL_API int ll_channel_decay(const void* z, int dtype, int stride, const float* bias, float tau, float* out, int M, int C,
+                            ll_stream stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Windowed attention with kept first tokens, soft cap, distance penalty and mixed heads (csrc/window_attn.cu)
+ * ------------------------------------------------------------------------------------- */
+
+/* Rows of this step into the cache [B][keep + ring][cols]: position j -> slot j (j < keep) or keep + (j - keep) % ring. */
+LL_API int ll_sink_ring_append(const void* k, int k_stride, const void* v, int v_stride, int dtype, const int32_t* pos_ids, void* kc,
+                               void* vc, int B, int T, int kcols, int vcols, int keep, int ring, ll_stream stream);
+/* s_h(i,j) = cap tanh(scale q_h(i).k_g(j) / cap) - r1_h ln(1 + r2_h (i-j)) (cap 0: none); j visible when j <= i and
+ * (i-j < window or j < keep); softmax per head; weights mixed over heads by talk [H][H]; o_h = sigmoid(gate[m][h]) *
+ * sum_j mixed_h(i,j) v_g(h)(j) -> y [B*T][H*vdim] (gate NULL: no gate).  scratch: ll_window_attn_scratch_bytes. */
+LL_API size_t ll_window_attn_scratch_bytes(int M, int H, int vdim, int splits);
+LL_API int ll_window_attn(const void* q, int q_stride, const void* gate, int gate_stride, const void* kc, const void* vc, int dtype,
+                          const int32_t* pos_ids, const float* r1, const float* r2, const float* talk, float scale, float softcap,
+                          int B, int T, int H, int G, int dim, int vdim, int window, int keep, int ring, int splits, float* scratch,
+                          void* y, ll_stream stream);
 
 #ifdef __cplusplus
 }

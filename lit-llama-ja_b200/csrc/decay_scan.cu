@@ -1,0 +1,212 @@
+// Linear recurrence with a diagonal decay: the state of selective state-space layers (one decay per head and token) and
+// of gated linear attention (one decay per key channel and token).  Per sequence b and head h, with S an n x p matrix:
+//
+//   S_t[i][c] = a_t[i] * S_(t-1)[i][c] + (ks_t * k_t[i]) * v_t[c]
+//   y_t[c]    = qs * sum_i q_t[i] * S_t[i][c]  +  skip[h] * v_t[c]
+//
+// q, k (n per head; `qk_heads` heads shared by consecutive groups of heads) and v (p per head) are column slices of
+// projection outputs in the activation dtype; a (the decay itself, in (0, 1]), ks and skip are fp32; S and y are fp32 and
+// every product and sum is fp32.  The state is carried in `state[B][H][n][p]`; a sequence at position 0 starts from zero
+// whatever the state holds.
+#include "common.cuh"
+
+namespace llb {
+
+constexpr int DS_THREADS = 128;
+constexpr int DS_NL = 16;       // state rows a thread keeps in registers
+// tokens staged per round (fewer when a head's state rows are many, so that the staging stays small)
+__host__ __device__ constexpr int ds_tc(int np) { return np <= 8 ? 16 : 4; }
+
+// grid (p tiles, H, B).  NP threads (consecutive lanes) share one column c and split the n rows; PT = DS_THREADS / NP
+// columns per block.
+template <typename T, int NP>
+__global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
+    const T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride, const T* __restrict__ v, int v_stride,
+    const float* __restrict__ a, int a_per_channel, const float* __restrict__ ks, const float* __restrict__ skip, float qs,
+    float* __restrict__ state, const int32_t* __restrict__ pos_ids, float* __restrict__ y, int Tn, int H, int qk_heads, int n,
+    int p) {
+  constexpr int PT = DS_THREADS / NP;
+  constexpr int NPAD = NP * DS_NL;
+  constexpr int DS_TC = ds_tc(NP);
+  __shared__ __align__(16) float s_a[DS_TC][NPAD], s_k[DS_TC][NPAD], s_q[DS_TC][NPAD];
+  __shared__ float s_v[DS_TC][PT];
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int g = h / (H / qk_heads);
+  const int part = threadIdx.x % NP, pl = threadIdx.x / NP;
+  const int c = blockIdx.x * PT + pl;
+  const bool live = c < p;
+  const int i0 = part * DS_NL;
+  float S[DS_NL];
+  float* sp = state + (((size_t)b * H + h) * n) * p;
+  const bool fresh = pos_ids[0] == 0;
+#pragma unroll
+  for (int i = 0; i < DS_NL; ++i) S[i] = (!fresh && live && i0 + i < n) ? sp[(size_t)(i0 + i) * p + c] : 0.f;
+  const float sk = skip ? skip[h] : 0.f;
+  for (int t0 = 0; t0 < Tn; t0 += DS_TC) {
+    const int nt = min(DS_TC, Tn - t0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * NPAD; idx += DS_THREADS) {
+      const int tt = idx / NPAD, i = idx - tt * NPAD;
+      const size_t m = (size_t)b * Tn + t0 + tt;
+      float av = 1.f, kv = 0.f, qv = 0.f;
+      if (i < n) {
+        av = a_per_channel ? a[(m * H + h) * n + i] : a[m * H + h];
+        kv = dt<T>::ld(k, m * k_stride + (size_t)g * n + i) * (ks ? ks[m * H + h] : 1.f);
+        qv = dt<T>::ld(q, m * q_stride + (size_t)g * n + i) * qs;
+      }
+      s_a[tt][i] = av;
+      s_k[tt][i] = kv;
+      s_q[tt][i] = qv;
+    }
+    for (int idx = threadIdx.x; idx < nt * PT; idx += DS_THREADS) {
+      const int tt = idx / PT, cc = idx - tt * PT;
+      const int col = blockIdx.x * PT + cc;
+      s_v[tt][cc] = col < p ? dt<T>::ld(v, ((size_t)b * Tn + t0 + tt) * v_stride + (size_t)h * p + col) : 0.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float vv = s_v[tt][pl];
+      float acc = 0.f;
+#pragma unroll
+      for (int i4 = 0; i4 < DS_NL; i4 += 4) {
+        const float4 a4 = *(const float4*)&s_a[tt][i0 + i4];
+        const float4 k4 = *(const float4*)&s_k[tt][i0 + i4];
+        const float4 q4 = *(const float4*)&s_q[tt][i0 + i4];
+        S[i4 + 0] = a4.x * S[i4 + 0] + k4.x * vv;
+        S[i4 + 1] = a4.y * S[i4 + 1] + k4.y * vv;
+        S[i4 + 2] = a4.z * S[i4 + 2] + k4.z * vv;
+        S[i4 + 3] = a4.w * S[i4 + 3] + k4.w * vv;
+        acc += q4.x * S[i4 + 0];
+        acc += q4.y * S[i4 + 1];
+        acc += q4.z * S[i4 + 2];
+        acc += q4.w * S[i4 + 3];
+      }
+#pragma unroll
+      for (int o = NP / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (part == 0 && live) y[((size_t)b * Tn + t0 + tt) * ((size_t)H * p) + (size_t)h * p + c] = acc + sk * vv;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < DS_NL; ++i)
+      if (i0 + i < n) sp[(size_t)(i0 + i) * p + c] = S[i];
+  }
+}
+
+template <typename T, int NP>
+static int decay_scan_launch(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, const float* a,
+                             int a_per_channel, const float* ks, const float* skip, float qs, float* state, const int32_t* pos_ids,
+                             float* y, int B, int Tn, int H, int qk_heads, int n, int p, cudaStream_t st) {
+  constexpr int PT = DS_THREADS / NP;
+  decay_scan_kernel<T, NP><<<dim3((p + PT - 1) / PT, H, B), DS_THREADS, 0, st>>>((const T*)q, q_stride, (const T*)k, k_stride,
+                                                                                (const T*)v, v_stride, a, a_per_channel, ks, skip,
+                                                                                qs, state, pos_ids, y, Tn, H, qk_heads, n, p);
+  LL_LAUNCH_OK("decay_scan_kernel");
+  return LL_OK;
+}
+
+// Step sizes and decays of a selective state-space layer: dt = softplus(raw + dt_bias[h]) (no clamp),
+// decay = exp(-exp(a_log[h]) * dt); raw is a column slice of the input projection's output.
+template <typename T>
+__global__ void ssm_gates_kernel(const T* __restrict__ raw, int stride, const float* __restrict__ dt_bias,
+                                 const float* __restrict__ a_log, float* __restrict__ dt_out, float* __restrict__ decay, int H,
+                                 size_t total) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t m = i / H;
+  const int h = (int)(i - m * H);
+  const float z = dt<T>::ld(raw, m * stride + h) + dt_bias[h];
+  const float d = z > 20.f ? z : log1pf(expf(z));
+  dt_out[i] = d;
+  decay[i] = expf(-expf(a_log[h]) * d);
+}
+
+// Decay per key channel of gated linear attention: sigmoid(z + bias)^(1/tau) = exp(-softplus(-(z + bias)) / tau).
+template <typename T>
+__global__ void channel_decay_kernel(const T* __restrict__ z, int stride, const float* __restrict__ bias, float inv_tau,
+                                     float* __restrict__ out, int C, size_t total) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t m = i / C;
+  const int c = (int)(i - m * C);
+  const float u = -(dt<T>::ld(z, m * stride + c) + (bias ? bias[c] : 0.f));
+  const float sp = u > 20.f ? u : log1pf(expf(u));
+  out[i] = expf(-sp * inv_tau);
+}
+
+}  // namespace llb
+
+using namespace llb;
+
+extern "C" {
+
+int ll_decay_scan(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, int dtype, const float* a,
+                  int a_per_channel, const float* ks, const float* skip, float qs, float* state, const int32_t* pos_ids, float* y,
+                  int B, int T, int H, int qk_heads, int n, int p, ll_stream stream) {
+  LL_CHECK_ARG(q && k && v && a && state && pos_ids && y, "decay_scan: null pointer");
+  LL_CHECK_ARG(B >= 0 && T >= 0 && H > 0 && qk_heads > 0 && H % qk_heads == 0 && n > 0 && p > 0, "bad decay_scan arguments");
+  if (n > 32 * DS_NL) {
+    set_error("decay_scan: %d state rows per head (up to %d)", n, 32 * DS_NL);
+    return LL_ERR_UNSUPPORTED;
+  }
+  if (B == 0 || T == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  int np = 1;
+  while (np * DS_NL < n) np *= 2;
+#define LL_DS(TT, NP)                                                                                                            \
+  return decay_scan_launch<TT, NP>(q, q_stride, k, k_stride, v, v_stride, a, a_per_channel, ks, skip, qs, state, pos_ids, y, B, T, \
+                                   H, qk_heads, n, p, st)
+#define LL_DS_T(TT)                 \
+  switch (np) {                     \
+    case 1: LL_DS(TT, 1);           \
+    case 2: LL_DS(TT, 2);           \
+    case 4: LL_DS(TT, 4);           \
+    case 8: LL_DS(TT, 8);           \
+    case 16: LL_DS(TT, 16);         \
+    default: LL_DS(TT, 32);         \
+  }
+  if (dtype == LL_F32) { LL_DS_T(float) }
+  if (dtype == LL_BF16) { LL_DS_T(__nv_bfloat16) }
+#undef LL_DS_T
+#undef LL_DS
+  set_error("decay_scan: unsupported dtype %d", dtype);
+  return LL_ERR_UNSUPPORTED;
+}
+
+int ll_ssm_gates(const void* raw, int dtype, int stride, const float* dt_bias, const float* a_log, float* dt_out, float* decay,
+                 int M, int H, ll_stream stream) {
+  LL_CHECK_ARG(raw && dt_bias && a_log && dt_out && decay && M >= 0 && H > 0 && stride >= H, "bad ssm_gates arguments");
+  const size_t total = (size_t)M * H;
+  if (total == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == LL_F32) ssm_gates_kernel<float><<<blocks, 256, 0, st>>>((const float*)raw, stride, dt_bias, a_log, dt_out, decay, H, total);
+  else if (dtype == LL_BF16)
+    ssm_gates_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)raw, stride, dt_bias, a_log, dt_out, decay, H, total);
+  else {
+    set_error("ssm_gates: unsupported dtype %d", dtype);
+    return LL_ERR_UNSUPPORTED;
+  }
+  LL_LAUNCH_OK("ssm_gates_kernel");
+  return LL_OK;
+}
+
+int ll_channel_decay(const void* z, int dtype, int stride, const float* bias, float tau, float* out, int M, int C,
+                     ll_stream stream) {
+  LL_CHECK_ARG(z && out && M >= 0 && C > 0 && stride >= C && tau > 0.f, "bad channel_decay arguments");
+  const size_t total = (size_t)M * C;
+  if (total == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == LL_F32) channel_decay_kernel<float><<<blocks, 256, 0, st>>>((const float*)z, stride, bias, 1.f / tau, out, C, total);
+  else if (dtype == LL_BF16)
+    channel_decay_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)z, stride, bias, 1.f / tau, out, C, total);
+  else {
+    set_error("channel_decay: unsupported dtype %d", dtype);
+    return LL_ERR_UNSUPPORTED;
+  }
+  LL_LAUNCH_OK("channel_decay_kernel");
+  return LL_OK;
+}
+
+}  // extern "C"

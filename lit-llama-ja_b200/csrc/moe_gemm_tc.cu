@@ -51,7 +51,7 @@ template <int MODE>
 __global__ void __launch_bounds__(192, 2) moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                                                              const __grid_constant__ CUtensorMap map_b,
                                                              const int32_t* __restrict__ offsets, const int32_t* __restrict__ perm,
-                                                             int X, int N, int K, float limit, float alpha,
+                                                             int X, int N, int K, float limit, float alpha, float shift,
                                                              __nv_bfloat16* __restrict__ c, int ldc) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~(uintptr_t)1023);
@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(192, 2) moe_gemm_tc_kernel(const __grid_consta
           for (int j = 0; j < 32; ++j) {
             const float g = fminf(__uint_as_float(v[j]), limit);
             const float up = fminf(fmaxf(__uint_as_float(u[j]), -limit), limit);
-            f[j] = g / (1.f + expf(-alpha * g)) * (up + 1.f);
+            f[j] = g / (1.f + expf(-alpha * g)) * (up + shift);
           }
         } else {
 #pragma unroll
@@ -196,7 +196,7 @@ __global__ void moe_gather_rows_kernel(const uint4* __restrict__ x, long long ld
 
 template <int MODE>
 int launch_moe_tc(const CUtensorMap& ma, const CUtensorMap& mb, const int32_t* offsets, const int32_t* perm, int X, int N, int K,
-                  float limit, float alpha, void* c, int ldc, int n_rows, cudaStream_t st) {
+                  float limit, float alpha, float shift, void* c, int ldc, int n_rows, cudaStream_t st) {
   constexpr size_t smem = (size_t)MT_STAGES * (MT_A_BYTES + MT_B_BYTES) + (2 * MT_STAGES + 1) * 8 + 32 + 1024;
   static bool configured = false;
   if (!configured) {
@@ -205,7 +205,7 @@ int launch_moe_tc(const CUtensorMap& ma, const CUtensorMap& mb, const int32_t* o
   }
   const int ncols = MODE == 1 ? MT_BN : 2 * MT_BN;
   dim3 grid((N + ncols - 1) / ncols, (n_rows + BM - 1) / BM + X);
-  moe_gemm_tc_kernel<MODE><<<grid, 192, smem, st>>>(ma, mb, offsets, perm, X, N, K, limit, alpha, (__nv_bfloat16*)c, ldc);
+  moe_gemm_tc_kernel<MODE><<<grid, 192, smem, st>>>(ma, mb, offsets, perm, X, N, K, limit, alpha, shift, (__nv_bfloat16*)c, ldc);
   LL_LAUNCH_OK("moe_gemm_tc_kernel");
   return LL_OK;
 }
@@ -231,7 +231,9 @@ int ll_moe_gather_rows(const void* x, int ldx, const int32_t* perm, int top, int
 int ll_moe_grouped_gemm_tc(const void* a, const void* w, const int32_t* offsets, const int32_t* perm, int mode, int n_rows,
                            int n_experts, int N, int K, float limit, float alpha, void* c, int ldc, ll_stream stream) {
   LL_CHECK_ARG(a && w && offsets && perm && c, "moe_grouped_gemm_tc: null pointer");
-  LL_CHECK_ARG(n_rows >= 0 && n_experts > 0 && N > 0 && K > 0 && ldc >= N && (mode == 0 || mode == 1), "bad moe_grouped_gemm_tc arguments");
+  LL_CHECK_ARG(n_rows >= 0 && n_experts > 0 && N > 0 && K > 0 && ldc >= N && mode >= 0 && mode <= 2, "bad moe_grouped_gemm_tc arguments");
+  const float shift = mode == 2 ? 0.f : 1.f;     // mode 2: the up branch enters as it is
+  if (mode == 2) mode = 1;
   LL_CHECK_ARG(K % 8 == 0 && ((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)c & 15) == 0,
                "moe_grouped_gemm_tc: K must be a multiple of 8 and the operands 16-byte aligned (TMA rows)");
   if (n_rows == 0) return LL_OK;
@@ -241,8 +243,8 @@ int ll_moe_grouped_gemm_tc(const void* a, const void* w, const int32_t* offsets,
   if (int r = make_map(a, n_rows, K, BM, &ma)) return r;
   if (int r = make_map(w, (int)wrows, K, MT_BN, &mb)) return r;
   cudaStream_t st = (cudaStream_t)stream;
-  if (mode == 1) return launch_moe_tc<1>(ma, mb, offsets, perm, n_experts, N, K, limit, alpha, c, ldc, n_rows, st);
-  return launch_moe_tc<0>(ma, mb, offsets, perm, n_experts, N, K, limit, alpha, c, ldc, n_rows, st);
+  if (mode == 1) return launch_moe_tc<1>(ma, mb, offsets, perm, n_experts, N, K, limit, alpha, shift, c, ldc, n_rows, st);
+  return launch_moe_tc<0>(ma, mb, offsets, perm, n_experts, N, K, limit, alpha, shift, c, ldc, n_rows, st);
 }
 
 // 0, or the code of the first bounded wait that ran out in a kernel of this file (1: ring slot, 2: operands, 3: accumulator).

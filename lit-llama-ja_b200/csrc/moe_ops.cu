@@ -3,9 +3,11 @@
 // a grouped GEMM over the sorted rows whose blocks find their expert from the device-side counts,
 // and the weighted combination with an optional always-on shared expert.
 //
-//   route    z = W_r x + b (fp32), the `top` largest logits, weights = softmax over the chosen logits
+//   route    z = W_r x + b (fp32), the `top` largest logits, weights = softmax over the chosen logits; or scores =
+//            softmax over ALL experts with weights = chosen scores / (their sum + 1e-20); optionally only experts of the
+//            `keep_groups` best of `n_groups` equal groups of neighbouring experts (a group's score: its largest) compete
 //   permute  rows sorted by expert: perm[offsets[e] + rank] = token * top + choice
-//   grouped  MODE_GLU : h[r][:] = glu(x[token(r)] . Wgu[e]^T)   (stacked [gate; up] weight, clamped GLU)
+//   grouped  MODE_GLU : h[r][:] = glu(x[token(r)] . Wgu[e]^T)   (stacked [gate; up] weight; g s(alpha g) (u + shift), clamped)
 //            MODE_DOWN: y[perm[r]][:] = h[r] . Wd[e]^T
 //   combine  out[m] = sum_k w[m][k] * y[m * top + k]  (+ sigmoid(s[m]) * shared[m])
 #include "common.cuh"
@@ -19,11 +21,13 @@ constexpr int RT_EG = 4;         // experts a warp accumulates side by side
 template <typename T>
 __global__ void __launch_bounds__(RT_THREADS) moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w_router,
                                                                const float* __restrict__ bias, int M, int dim, int X, int top,
+                                                               int score_all, int n_groups, int keep_groups,
                                                                int32_t* __restrict__ expert_idx, float* __restrict__ expert_w,
                                                                int32_t* __restrict__ counts, int32_t* __restrict__ rank) {
   extern __shared__ float sm[];
   float* xs = sm;                      // [RT_TOK][dim]
   float* zs = xs + RT_TOK * dim;       // [RT_TOK][X]
+  float* gms = zs + RT_TOK * X;        // [RT_TOK][n_groups] group maxima, then [RT_TOK][n_groups] "may compete" flags
   const int m0 = blockIdx.x * RT_TOK;
   const int nt = min(RT_TOK, M - m0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -78,6 +82,34 @@ __global__ void __launch_bounds__(RT_THREADS) moe_route_kernel(const T* __restri
     float* z = zs + warp * X;
     const int m = m0 + warp;
     float v0 = 0.f, denom = 0.f;
+    float zmax = -INFINITY, zsum = 1.f;
+    if (score_all) {                   // softmax over every expert, also those that cannot be chosen
+      for (int e = lane; e < X; e += 32) zmax = fmaxf(zmax, z[e]);
+      zmax = warp_max(zmax);
+      float acc = 0.f;
+      for (int e = lane; e < X; e += 32) acc += expf(z[e] - zmax);
+      zsum = warp_sum(acc);
+    }
+    if (n_groups > 1 && keep_groups < n_groups) {
+      float* gm = gms + warp * n_groups;
+      float* ga = gms + RT_TOK * n_groups + warp * n_groups;
+      const int gs = X / n_groups;
+      for (int g = lane; g < n_groups; g += 32) {
+        float mx = -INFINITY;
+        for (int e = g * gs; e < (g + 1) * gs; ++e) mx = fmaxf(mx, z[e]);
+        gm[g] = mx;
+      }
+      __syncwarp();
+      for (int g = lane; g < n_groups; g += 32) {      // a group competes when fewer than keep_groups groups beat it
+        int before = 0;
+        for (int o = 0; o < n_groups; ++o) before += (gm[o] > gm[g] || (gm[o] == gm[g] && o < g)) ? 1 : 0;
+        ga[g] = before < keep_groups ? 1.f : 0.f;
+      }
+      __syncwarp();
+      for (int e = lane; e < X; e += 32)
+        if (ga[e / gs] == 0.f) z[e] = -INFINITY;
+      __syncwarp();
+    }
     for (int k = 0; k < top; ++k) {
       float best = -INFINITY;
       int bi = 0x7fffffff;
@@ -92,7 +124,7 @@ __global__ void __launch_bounds__(RT_THREADS) moe_route_kernel(const T* __restri
         if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
       }
       if (k == 0) v0 = best;
-      const float p = expf(best - v0);
+      const float p = score_all ? expf(best - zmax) / zsum : expf(best - v0);
       denom += p;
       if (lane == 0) {
         z[bi] = -INFINITY;
@@ -103,6 +135,7 @@ __global__ void __launch_bounds__(RT_THREADS) moe_route_kernel(const T* __restri
       __syncwarp();
     }
     __syncwarp();
+    if (score_all) denom += 1e-20f;
     for (int k = lane; k < top; k += 32) expert_w[(size_t)m * top + k] /= denom;
   }
 }
@@ -132,7 +165,7 @@ template <typename T, int TM, int MODE>
 __global__ void __launch_bounds__(GG_THREADS) moe_grouped_gemm_kernel(const T* __restrict__ a, int lda, const T* __restrict__ w,
                                                                       const int32_t* __restrict__ offsets,
                                                                       const int32_t* __restrict__ perm, int top, int X, int N,
-                                                                      int K, float limit, float alpha, T* __restrict__ c, int ldc) {
+                                                                      int K, float limit, float alpha, float shift, T* __restrict__ c, int ldc) {
   constexpr int BM = 16 * TM;
   constexpr int NB = MODE == MODE_GLU ? 2 : 1;
   __shared__ float As[GG_BK][BM + 1];
@@ -205,7 +238,7 @@ __global__ void __launch_bounds__(GG_THREADS) moe_grouped_gemm_kernel(const T* _
       if (MODE == MODE_GLU) {
         const float g = fminf(acc[0][i][j], limit);
         const float u = fminf(fmaxf(acc[NB - 1][i][j], -limit), limit);
-        v = g / (1.f + expf(-alpha * g)) * (u + 1.f);
+        v = g / (1.f + expf(-alpha * g)) * (u + shift);
       } else {
         v = acc[0][i][j];
       }
@@ -237,7 +270,8 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
 template <int BM, int MODE>
 __global__ void __launch_bounds__(GM_THREADS) moe_grouped_gemm_mma_kernel(
     const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, const int32_t* __restrict__ offsets,
-    const int32_t* __restrict__ perm, int top, int X, int N, int K, float limit, float alpha, __nv_bfloat16* __restrict__ c, int ldc) {
+    const int32_t* __restrict__ perm, int top, int X, int N, int K, float limit, float alpha, float shift,
+    __nv_bfloat16* __restrict__ c, int ldc) {
   constexpr int NB = MODE == MODE_GLU ? 2 : 1;
   constexpr int ST = gm_stages(BM);
   constexpr int WARPS_M = BM >= 32 ? 2 : 1, WARPS_N = 4 / WARPS_M;
@@ -335,7 +369,7 @@ __global__ void __launch_bounds__(GM_THREADS) moe_grouped_gemm_mma_kernel(
         if (MODE == MODE_GLU) {
           const float g = fminf(acc[0][i][j][q], limit);
           const float u = fminf(fmaxf(acc[NB - 1][i][j][q], -limit), limit);
-          v = g / (1.f + expf(-alpha * g)) * (u + 1.f);
+          v = g / (1.f + expf(-alpha * g)) * (u + shift);
         } else {
           v = acc[0][i][j][q];
         }
@@ -345,7 +379,7 @@ __global__ void __launch_bounds__(GM_THREADS) moe_grouped_gemm_mma_kernel(
 
 template <int BM, int MODE>
 static int launch_grouped_mma(const void* a, int lda, const void* w, const int32_t* offsets, const int32_t* perm, int top, int X, int N,
-                              int K, float limit, float alpha, void* c, int ldc, int n_rows, cudaStream_t st) {
+                              int K, float limit, float alpha, float shift, void* c, int ldc, int n_rows, cudaStream_t st) {
   constexpr int NB = MODE == MODE_GLU ? 2 : 1;
   const size_t smem = sizeof(__nv_bfloat16) * gm_stages(BM) * (BM + NB * GM_BN) * GM_PITCH;
   static bool once = false;
@@ -355,7 +389,7 @@ static int launch_grouped_mma(const void* a, int lda, const void* w, const int32
   }
   dim3 grid((n_rows + BM - 1) / BM + X, (N + GM_BN - 1) / GM_BN);
   moe_grouped_gemm_mma_kernel<BM, MODE><<<grid, GM_THREADS, smem, st>>>((const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, offsets, perm,
-                                                                       top, X, N, K, limit, alpha, (__nv_bfloat16*)c, ldc);
+                                                                       top, X, N, K, limit, alpha, shift, (__nv_bfloat16*)c, ldc);
   LL_LAUNCH_OK("moe_grouped_gemm_mma_kernel");
   return LL_OK;
 }
@@ -377,11 +411,11 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const float* __restr
 
 template <typename T, int TM, int MODE>
 static int launch_grouped(const void* a, int lda, const void* w, const int32_t* offsets, const int32_t* perm, int top, int X, int N,
-                          int K, float limit, float alpha, void* c, int ldc, int n_rows, cudaStream_t st) {
+                          int K, float limit, float alpha, float shift, void* c, int ldc, int n_rows, cudaStream_t st) {
   constexpr int BM = 16 * TM;
   dim3 grid((n_rows + BM - 1) / BM + X, (N + GG_BN - 1) / GG_BN);
   moe_grouped_gemm_kernel<T, TM, MODE><<<grid, GG_THREADS, 0, st>>>((const T*)a, lda, (const T*)w, offsets, perm, top, X, N, K, limit,
-                                                                   alpha, (T*)c, ldc);
+                                                                   alpha, shift, (T*)c, ldc);
   LL_LAUNCH_OK("moe_grouped_gemm_kernel");
   return LL_OK;
 }
@@ -395,11 +429,21 @@ extern "C" {
 int ll_moe_route(const void* x, int dtype, const float* w_router, const float* bias, int M, int dim, int n_experts, int top,
                  int32_t* expert_idx, float* expert_w, int32_t* counts, int32_t* rank, int32_t* offsets, int32_t* perm,
                  ll_stream stream) {
+  return ll_moe_route_scored(x, dtype, w_router, bias, M, dim, n_experts, top, 0, 1, 1, expert_idx, expert_w, counts, rank, offsets,
+                             perm, stream);
+}
+
+int ll_moe_route_scored(const void* x, int dtype, const float* w_router, const float* bias, int M, int dim, int n_experts, int top,
+                        int score_all, int n_groups, int keep_groups, int32_t* expert_idx, float* expert_w, int32_t* counts,
+                        int32_t* rank, int32_t* offsets, int32_t* perm, ll_stream stream) {
   LL_CHECK_ARG(x && w_router && expert_idx && expert_w && counts && rank && offsets && perm, "moe_route: null pointer");
   LL_CHECK_ARG(M >= 0 && dim > 0 && n_experts > 0 && top > 0 && top <= n_experts, "bad moe_route arguments");
+  LL_CHECK_ARG(n_groups >= 1 && keep_groups >= 1 && keep_groups <= n_groups && n_experts % n_groups == 0 &&
+                   top <= keep_groups * (n_experts / n_groups),
+               "moe_route: %d groups (keep %d) of %d experts cannot give %d choices", n_groups, keep_groups, n_experts, top);
   if (M == 0) return LL_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  const size_t smem = sizeof(float) * RT_TOK * ((size_t)dim + n_experts);
+  const size_t smem = sizeof(float) * RT_TOK * ((size_t)dim + n_experts + 2 * (size_t)n_groups);
   if (smem > 200 * 1024) {
     set_error("moe_route: width %d with %d experts does not fit shared memory", dim, n_experts);
     return LL_ERR_UNSUPPORTED;
@@ -408,12 +452,13 @@ int ll_moe_route(const void* x, int dtype, const float* w_router, const float* b
   const int blocks = (M + RT_TOK - 1) / RT_TOK;
   if (dtype == LL_F32) {
     LL_CUDA(cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    moe_route_kernel<float><<<blocks, RT_THREADS, smem, st>>>((const float*)x, w_router, bias, M, dim, n_experts, top, expert_idx,
-                                                             expert_w, counts, rank);
+    moe_route_kernel<float><<<blocks, RT_THREADS, smem, st>>>((const float*)x, w_router, bias, M, dim, n_experts, top, score_all,
+                                                             n_groups, keep_groups, expert_idx, expert_w, counts, rank);
   } else if (dtype == LL_BF16) {
     LL_CUDA(cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     moe_route_kernel<__nv_bfloat16><<<blocks, RT_THREADS, smem, st>>>((const __nv_bfloat16*)x, w_router, bias, M, dim, n_experts, top,
-                                                                     expert_idx, expert_w, counts, rank);
+                                                                     score_all, n_groups, keep_groups, expert_idx, expert_w, counts,
+                                                                     rank);
   } else {
     set_error("moe_route: unsupported dtype %d", dtype);
     return LL_ERR_UNSUPPORTED;
@@ -430,23 +475,25 @@ int ll_moe_grouped_gemm(const void* a, int lda, const void* w, const int32_t* of
                         int n_rows, int top, int n_experts, int N, int K, float limit, float alpha, void* c, int ldc,
                         ll_stream stream) {
   LL_CHECK_ARG(a && w && offsets && perm && c, "moe_grouped_gemm: null pointer");
-  LL_CHECK_ARG(n_rows >= 0 && top > 0 && n_experts > 0 && N > 0 && K > 0 && lda >= K && ldc >= N && (mode == 0 || mode == 1),
+  LL_CHECK_ARG(n_rows >= 0 && top > 0 && n_experts > 0 && N > 0 && K > 0 && lda >= K && ldc >= N && mode >= 0 && mode <= 2,
                "bad moe_grouped_gemm arguments");
   if (n_rows == 0) return LL_OK;
+  const float shift = mode == 2 ? 0.f : 1.f;     // mode 2: the up branch enters as it is
+  if (mode == 2) mode = MODE_GLU;
   cudaStream_t st = (cudaStream_t)stream;
   const bool small = n_rows <= 16 * n_experts / 2 + 16;   // few rows per expert: narrow row tiles waste less
 #define LL_GG(T)                                                                                                              \
-  (mode == MODE_GLU ? (small ? launch_grouped<T, 1, MODE_GLU>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st)  \
-                             : launch_grouped<T, 4, MODE_GLU>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st)) \
-                    : (small ? launch_grouped<T, 1, MODE_DOWN>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st) \
-                             : launch_grouped<T, 4, MODE_DOWN>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st)))
+  (mode == MODE_GLU ? (small ? launch_grouped<T, 1, MODE_GLU>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, shift, c, ldc, n_rows, st)  \
+                             : launch_grouped<T, 4, MODE_GLU>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, shift, c, ldc, n_rows, st)) \
+                    : (small ? launch_grouped<T, 1, MODE_DOWN>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, shift, c, ldc, n_rows, st) \
+                             : launch_grouped<T, 4, MODE_DOWN>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, shift, c, ldc, n_rows, st)))
   if (dtype == LL_F32) return LL_GG(float);
   if (dtype == LL_BF16 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0) {
     if (mode == MODE_GLU)
-      return small ? launch_grouped_mma<16, MODE_GLU>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st)
-                   : launch_grouped_mma<64, MODE_GLU>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st);
-    return small ? launch_grouped_mma<16, MODE_DOWN>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st)
-                 : launch_grouped_mma<64, MODE_DOWN>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, c, ldc, n_rows, st);
+      return small ? launch_grouped_mma<16, MODE_GLU>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, shift, c, ldc, n_rows, st)
+                   : launch_grouped_mma<64, MODE_GLU>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, shift, c, ldc, n_rows, st);
+    return small ? launch_grouped_mma<16, MODE_DOWN>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, shift, c, ldc, n_rows, st)
+                 : launch_grouped_mma<64, MODE_DOWN>(a, lda, w, offsets, perm, top, n_experts, N, K, limit, alpha, shift, c, ldc, n_rows, st);
   }
   if (dtype == LL_BF16) return LL_GG(__nv_bfloat16);
 #undef LL_GG

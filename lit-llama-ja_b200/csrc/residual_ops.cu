@@ -157,3 +157,149 @@ int ll_glu_clamp(const void* gu, int gu_stride, int ff, float limit, float alpha
 }
 
 }  // extern "C"
+
+// ---- two-branch layers on an fp32 stream: x += sum of branch outputs, then two norms of the same x -----------------
+namespace llb {
+
+// x[m][:] += s0 * a0 + s1 * a1 + s2 * a2 (each optional, activation dtype TA), in place, fp32.  Then, with
+// n = x / sqrt(mean(x^2) + eps):  out1 = n * w1 (fp32 or TA, see out1_f32; optional), out2 = n * w2 (TA; optional).
+template <typename TA>
+__global__ void add_norm_pair_kernel(float* __restrict__ x, const TA* __restrict__ a0, float s0, const TA* __restrict__ a1,
+                                     float s1, const TA* __restrict__ a2, float s2, const float* __restrict__ w1,
+                                     const float* __restrict__ w2, float eps, void* __restrict__ out1, int out1_f32,
+                                     TA* __restrict__ out2, int dim) {
+  __shared__ float red[32];
+  const size_t base = (size_t)blockIdx.x * dim;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float v = x[base + i];
+    if (a0 || a1 || a2) {
+      float add = 0.f;
+      if (a0) add += s0 * dt<TA>::ld(a0, base + i);
+      if (a1) add += s1 * dt<TA>::ld(a1, base + i);
+      if (a2) add += s2 * dt<TA>::ld(a2, base + i);
+      v += add;
+      x[base + i] = v;
+    }
+    ss += v * v;
+  }
+  if (!out1 && !out2) return;
+  ss = block_sum(ss, red);
+  const float k = 1.f / sqrtf(ss / (float)dim + eps);
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float n = x[base + i] * k;
+    if (out1) {
+      if (out1_f32) ((float*)out1)[base + i] = n * w1[i];
+      else dt<TA>::st((TA*)out1, base + i, n * w1[i]);
+    }
+    if (out2) dt<TA>::st(out2, base + i, n * w2[i]);
+  }
+}
+
+// RMS norm of an fp32 row in `groups` equal parts (each by its own root mean square), a weight, and a silu gate:
+//   gate_first: t = y * silu(g);  out = t / rms_part(t) * w          (the gate enters the norm)
+//   otherwise : out = y / rms_part(y) * w * silu(g)                  (the gate follows the norm)
+// w has C entries, or C / groups entries shared by the parts (w_shared).  One block per row.
+template <typename TA>
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, const TA* __restrict__ gate, int gate_stride,
+                                        const float* __restrict__ w, int w_shared, float eps, int groups, int gate_first,
+                                        TA* __restrict__ out, int C) {
+  const int m = blockIdx.x;
+  const int gs = C / groups;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int g = warp; g < groups; g += nw) {
+    const float* yr = y + (size_t)m * C + (size_t)g * gs;
+    const TA* gr = gate + (size_t)m * gate_stride + (size_t)g * gs;
+    float ss = 0.f;
+    for (int i = lane; i < gs; i += 32) {
+      float v = yr[i];
+      if (gate_first) {
+        const float z = dt<TA>::ld(gr, i);
+        v *= z / (1.f + expf(-z));
+      }
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    const float k = 1.f / sqrtf(ss / (float)gs + eps);
+    for (int i = lane; i < gs; i += 32) {
+      const float z = dt<TA>::ld(gr, i);
+      const float sg = z / (1.f + expf(-z));
+      const float wv = w[w_shared ? i : g * gs + i];
+      const float v = gate_first ? (yr[i] * sg) * k * wv : yr[i] * k * wv * sg;
+      dt<TA>::st(out, (size_t)m * C + (size_t)g * gs + i, v);
+    }
+  }
+}
+
+// in place: relu(v)^2
+template <typename T>
+__global__ void relu_squared_kernel(T* __restrict__ h, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = fmaxf(dt<T>::ld(h, i), 0.f);
+  dt<T>::st(h, i, v * v);
+}
+
+}  // namespace llb
+
+extern "C" {
+
+int ll_add_norm_pair(float* x, const void* a0, float s0, const void* a1, float s1, const void* a2, float s2, const float* w1,
+                     const float* w2, float eps, void* out1, int out1_f32, void* out2, int act_dtype, int rows, int dim,
+                     ll_stream stream) {
+  LL_CHECK_ARG(x && rows >= 0 && dim > 0 && (!out1 || w1) && (!out2 || w2), "bad add_norm_pair arguments");
+  if (rows == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int threads = dim >= 2048 ? 512 : dim >= 512 ? 256 : 128;
+  if (act_dtype == LL_F32)
+    add_norm_pair_kernel<float><<<rows, threads, 0, st>>>(x, (const float*)a0, s0, (const float*)a1, s1, (const float*)a2, s2, w1, w2,
+                                                         eps, out1, out1_f32, (float*)out2, dim);
+  else if (act_dtype == LL_BF16)
+    add_norm_pair_kernel<__nv_bfloat16><<<rows, threads, 0, st>>>(x, (const __nv_bfloat16*)a0, s0, (const __nv_bfloat16*)a1, s1,
+                                                                 (const __nv_bfloat16*)a2, s2, w1, w2, eps, out1, out1_f32,
+                                                                 (__nv_bfloat16*)out2, dim);
+  else {
+    set_error("add_norm_pair: unsupported dtype %d", act_dtype);
+    return LL_ERR_UNSUPPORTED;
+  }
+  LL_LAUNCH_OK("add_norm_pair_kernel");
+  return LL_OK;
+}
+
+int ll_gated_group_norm(const float* y, const void* gate, int gate_stride, const float* w, int w_shared, float eps, int groups,
+                        int gate_first, void* out, int act_dtype, int rows, int C, ll_stream stream) {
+  LL_CHECK_ARG(y && gate && w && out && rows >= 0 && C > 0 && groups > 0 && C % groups == 0 && gate_stride >= C,
+               "bad gated_group_norm arguments");
+  if (rows == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int threads = groups >= 8 ? 256 : groups >= 4 ? 128 : 32 * groups;
+  if (act_dtype == LL_F32)
+    gated_group_norm_kernel<float><<<rows, threads, 0, st>>>(y, (const float*)gate, gate_stride, w, w_shared, eps, groups, gate_first,
+                                                            (float*)out, C);
+  else if (act_dtype == LL_BF16)
+    gated_group_norm_kernel<__nv_bfloat16><<<rows, threads, 0, st>>>(y, (const __nv_bfloat16*)gate, gate_stride, w, w_shared, eps,
+                                                                    groups, gate_first, (__nv_bfloat16*)out, C);
+  else {
+    set_error("gated_group_norm: unsupported dtype %d", act_dtype);
+    return LL_ERR_UNSUPPORTED;
+  }
+  LL_LAUNCH_OK("gated_group_norm_kernel");
+  return LL_OK;
+}
+
+int ll_relu_squared(void* h, int dtype, size_t n, ll_stream stream) {
+  LL_CHECK_ARG(h, "relu_squared: null pointer");
+  if (n == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (dtype == LL_F32) relu_squared_kernel<float><<<blocks, 256, 0, st>>>((float*)h, n);
+  else if (dtype == LL_BF16) relu_squared_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((__nv_bfloat16*)h, n);
+  else {
+    set_error("relu_squared: unsupported dtype %d", dtype);
+    return LL_ERR_UNSUPPORTED;
+  }
+  LL_LAUNCH_OK("relu_squared_kernel");
+  return LL_OK;
+}
+
+}  // extern "C"

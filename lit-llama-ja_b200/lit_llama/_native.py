@@ -115,15 +115,28 @@ EXPORTS = {
                         i32, C.c_float, i32, vp, vp], C.c_int),
     "ll_latent_attn_scratch_bytes": ([i32, i32, i32, i32], sz_t),
     "ll_moe_route": ([vp, i32, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp], C.c_int),
+    "ll_moe_route_scored": ([vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp], C.c_int),
     "ll_moe_grouped_gemm": ([vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, C.c_float, C.c_float, vp, i32, vp], C.c_int),
     "ll_moe_gather_rows": ([vp, i32, vp, i32, i32, i32, vp, vp], C.c_int),
     "ll_moe_grouped_gemm_tc": ([vp, vp, vp, vp, i32, i32, i32, i32, i32, C.c_float, C.c_float, vp, i32, vp], C.c_int),
     "ll_moe_tc_error": ([], C.c_int),
     "ll_moe_combine": ([vp, vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, vp], C.c_int),
+    "ll_add_norm_pair": ([vp, vp, C.c_float, vp, C.c_float, vp, C.c_float, vp, vp, C.c_float, vp, i32, vp, i32, i32, i32, vp], C.c_int),
+    "ll_gated_group_norm": ([vp, vp, i32, vp, i32, C.c_float, i32, i32, vp, i32, i32, i32, vp], C.c_int),
+    "ll_relu_squared": ([vp, i32, sz_t, vp], C.c_int),
+    "ll_short_conv": ([vp, i32, i32, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp], C.c_int),
+    "ll_decay_scan": ([vp, i32, vp, i32, vp, i32, i32, vp, i32, vp, vp, C.c_float, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
+                      C.c_int),
+    "ll_ssm_gates": ([vp, i32, i32, vp, vp, vp, vp, i32, i32, vp], C.c_int),
+    "ll_channel_decay": ([vp, i32, i32, vp, C.c_float, vp, i32, i32, vp], C.c_int),
+    "ll_sink_ring_append": ([vp, i32, vp, i32, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp], C.c_int),
+    "ll_window_attn_scratch_bytes": ([i32, i32, i32, i32], sz_t),
+    "ll_window_attn": ([vp, i32, vp, i32, vp, vp, i32, vp, vp, vp, vp, C.c_float, C.c_float, i32, i32, i32, i32, i32, i32, i32, i32,
+                        i32, i32, vp, vp, vp], C.c_int),
 }
 _fn = {name: _proto(name, a, r) for name, (a, r) in EXPORTS.items()}
 
-ABI_VERSION = 12
+ABI_VERSION = 13
 if _fn["ll_abi_version"]() != ABI_VERSION:
     raise ImportError("libllb200.so ABI version mismatch; rebuild with lit-llama-ja_b200/build.py")
 
@@ -239,3 +252,9 @@ class Workspace:
         if attn_counters > self.attn_counters.numel():
             self.attn_counters = torch.zeros(attn_counters, dtype=torch.int32, device=self.device)
         return self
+
+
+def ptr_at(t: torch.Tensor, elem_offset: int) -> C.c_void_p:
+    """Address of element ``elem_offset`` (counted in elements of ``t``'s dtype) past ``t``'s first: a column slice of a
+    row-major matrix handed to a kernel that takes the row stride separately."""
+    return C.c_void_p(t.data_ptr() + elem_offset * t.element_size())

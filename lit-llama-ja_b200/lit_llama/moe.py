@@ -1,7 +1,12 @@
-"""Mixture-of-experts feed-forward with clamped gated-linear-unit experts and an optional always-on shared expert.
+"""Mixture-of-experts feed-forward with gated-linear-unit experts and an optional always-on shared expert.
 
-    z = W_r h + b  (fp32)      the ``top`` largest logits choose the experts, weights = softmax over the chosen logits
-    expert(h) = W_down( g * sigmoid(alpha * g) * (u + 1) ),  g = min(W_gate h, limit),  u = clamp(W_up h, -limit, limit)
+    z = W_r h + b  (fp32)      the ``top`` largest logits choose the experts
+    weights: softmax over the chosen logits (``score`` "chosen"), or the chosen entries of the softmax over ALL experts
+             divided by their sum + 1e-20 (``score`` "all")
+    groups:  the experts form ``groups`` equal groups of neighbours; only experts of the ``keep_groups`` groups with the
+             largest best expert can be chosen
+    expert(h) = W_down( g * sigmoid(alpha * g) * (u + up_shift) ),  g = min(W_gate h, limit),  u = clamp(W_up h, -limit, limit)
+                (limit inf, alpha 1, up_shift 0: the plain silu-gated unit)
     y = sum_k w_k expert_k(h)  +  sigmoid(w_sg . h) * shared(h)
 
 The experts' weights are stacked ([X, 2 ff, width] for [gate; up], [X, width, ff] for down) and run as two grouped GEMMs
@@ -40,6 +45,10 @@ class MoESpec:
     shared_gate: bool = True             # the shared expert is scaled by sigmoid(w_sg . h)
     router_bias: bool = True
     alpha: float = 1.702                 # slope inside the sigmoid of the gated unit
+    up_shift: float = 1.0                # the up branch enters as (u + up_shift): 1 or 0
+    score: str = "chosen"                # "chosen": softmax over the chosen logits; "all": over all experts, renormalised
+    groups: int = 1                      # equal groups of neighbouring experts
+    keep_groups: int = 1                 # groups whose experts can be chosen (groups == 1: all)
 
 
 def glu_clamp(gu: torch.Tensor, ff: int, limit: float, alpha: float) -> torch.Tensor:
@@ -56,6 +65,12 @@ class MoE(nn.Module):
         s = self.spec = spec
         if not 0 < s.top <= s.experts:
             raise ValueError(f"top {s.top} of {s.experts} experts")
+        if s.up_shift not in (0.0, 1.0) or s.score not in ("chosen", "all"):
+            raise ValueError(f"up_shift {s.up_shift} (0 or 1), score {s.score!r} ('chosen' or 'all')")
+        if s.groups < 1 or s.experts % s.groups or not 1 <= s.keep_groups <= s.groups \
+                or s.top > s.keep_groups * (s.experts // s.groups):
+            raise ValueError(f"{s.experts} experts in {s.groups} groups, {s.keep_groups} kept, cannot give {s.top} choices")
+        self.glu_mode = 1 if s.up_shift == 1.0 else 2
         kw = dict(dtype=dtype, device=device)
         f32 = dict(dtype=torch.float32, device=device)
         self.w_router = nn.Parameter(torch.empty((s.experts, s.width), **f32), requires_grad=False)
@@ -95,8 +110,9 @@ class MoE(nn.Module):
         w = torch.empty((M, s.top), dtype=torch.float32, device=dev)
         counts, rank = torch.empty(s.experts, **i32), torch.empty(M * s.top, **i32)
         offsets, perm = torch.empty(s.experts + 1, **i32), torch.empty(M * s.top, **i32)
-        N.call("ll_moe_route", N.ptr(x_act), N.dtype_code(x_act.dtype), N.ptr(self.w_router), N.ptr(self.b_router), M, s.width,
-               s.experts, s.top, N.ptr(idx), N.ptr(w), N.ptr(counts), N.ptr(rank), N.ptr(offsets), N.ptr(perm), N.stream())
+        N.call("ll_moe_route_scored", N.ptr(x_act), N.dtype_code(x_act.dtype), N.ptr(self.w_router), N.ptr(self.b_router), M, s.width,
+               s.experts, s.top, 1 if s.score == "all" else 0, s.groups, s.keep_groups if s.groups > 1 else 1, N.ptr(idx), N.ptr(w),
+               N.ptr(counts), N.ptr(rank), N.ptr(offsets), N.ptr(perm), N.stream())
         return idx, w, offsets, perm
 
     def takes_tensor_cores(self, n_rows: int, x_act: torch.Tensor) -> bool:
@@ -117,13 +133,13 @@ class MoE(nn.Module):
         if self.takes_tensor_cores(n, x_act):
             xs = torch.empty((n, s.width), dtype=dtype, device=dev)
             N.call("ll_moe_gather_rows", N.ptr(x_act), x_act.stride(0), N.ptr(perm), s.top, n, s.width, N.ptr(xs), st)
-            N.call("ll_moe_grouped_gemm_tc", N.ptr(xs), N.ptr(self.w_gu), N.ptr(offsets), N.ptr(perm), 1, n, s.experts, s.ff, s.width,
-                   float(s.limit), float(s.alpha), N.ptr(h), s.ff, st)
+            N.call("ll_moe_grouped_gemm_tc", N.ptr(xs), N.ptr(self.w_gu), N.ptr(offsets), N.ptr(perm), self.glu_mode, n, s.experts, s.ff,
+                   s.width, float(s.limit), float(s.alpha), N.ptr(h), s.ff, st)
             N.call("ll_moe_grouped_gemm_tc", N.ptr(h), N.ptr(self.w_down), N.ptr(offsets), N.ptr(perm), 0, n, s.experts, s.width, s.ff,
                    0.0, 0.0, N.ptr(y), s.width, st)
         else:
-            N.call("ll_moe_grouped_gemm", N.ptr(x_act), x_act.stride(0), N.ptr(self.w_gu), N.ptr(offsets), N.ptr(perm), 1, dt, n,
-                   s.top, s.experts, s.ff, s.width, float(s.limit), float(s.alpha), N.ptr(h), s.ff, st)
+            N.call("ll_moe_grouped_gemm", N.ptr(x_act), x_act.stride(0), N.ptr(self.w_gu), N.ptr(offsets), N.ptr(perm), self.glu_mode,
+                   dt, n, s.top, s.experts, s.ff, s.width, float(s.limit), float(s.alpha), N.ptr(h), s.ff, st)
             N.call("ll_moe_grouped_gemm", N.ptr(h), s.ff, N.ptr(self.w_down), N.ptr(offsets), N.ptr(perm), 0, dt, n, s.top, s.experts,
                    s.width, s.ff, 0.0, 0.0, N.ptr(y), s.width, st)
         ys = gate = None

@@ -18,6 +18,14 @@ FLAGS = [
 ]
 
 
+# The kernels a folder-loaded model family is served with (build_only): what a first run in a fresh checkout has to compile
+# for that family, and no more.  quant_pack carries the library's error plumbing and version.
+FAMILY_SOURCES = {
+    "Lepalorn": ["quant_pack", "decode_ops", "sampling", "residual_ops", "latent_attn", "moe_ops", "moe_gemm_tc"],
+    "Bededra": ["quant_pack", "residual_ops", "short_conv", "decay_scan", "window_attn", "moe_ops", "moe_gemm_tc"],
+}
+
+
 def sources():
     return sorted(CSRC.glob("*.cu"))
 

@@ -31,6 +31,10 @@ def _builtin() -> None:
         from .lepalorn import ARCHITECTURE, Lepalorn
 
         register_architecture(ARCHITECTURE, Lepalorn.from_dir)
+    if "Bededra" not in _FROM_DIR:
+        from .bededra import ARCHITECTURE, Bededra
+
+        register_architecture(ARCHITECTURE, Bededra.from_dir)
 
 
 def load_model_dir(path, dtype: torch.dtype = torch.bfloat16, device="cuda"):

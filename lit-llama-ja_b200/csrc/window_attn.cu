@@ -96,7 +96,7 @@ __device__ __forceinline__ void wa_load_q(const WaParams& P, int m, float* qs) {
   }
 }
 
-// shared memory: qs[H * dimp] | ss[H * kchunk] | pm[H * kchunk] | mh[H] | lh[H] | kv[kchunk * max(kpitch, vpitch)]
+// shared memory: qs[H * dimp] | ss[H * kchunk] | pm[H * kchunk] | mh[H up to 4] | lh[H up to 4] | kv[kchunk * max(kpitch, vpitch)]
 template <typename T>
 __global__ void __launch_bounds__(WA_THREADS) window_attn_stats_kernel(WaParams P) {
   extern __shared__ __align__(16) float wa_sm[];
@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_stats_kernel(WaParams 
   float* ss = qs + P.H * P.dimp;
   float* pm = ss + P.H * P.kchunk;
   float* mh = pm + P.H * P.kchunk;
-  float* lh = mh + P.H;
+  float* lh = mh + ((P.H + 3) / 4) * 4;     // every region starts on a 16-byte boundary
   float* kv = lh + ((P.H + 3) / 4) * 4;
   const int m = blockIdx.x, split = blockIdx.y;
   const int b = m / P.T, t = m - b * P.T;
@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_out_kernel(WaParams P)
   float* ss = qs + P.H * P.dimp;
   float* pm = ss + P.H * P.kchunk;
   float* mh = pm + P.H * P.kchunk;
-  float* lh = mh + P.H;
+  float* lh = mh + ((P.H + 3) / 4) * 4;     // every region starts on a 16-byte boundary
   float* kv = lh + ((P.H + 3) / 4) * 4;
   const int m = blockIdx.x, split = blockIdx.y;
   const int M = P.B * P.T;

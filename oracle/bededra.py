@@ -80,6 +80,31 @@ def visible(i, j, window, keep_first):
     return j <= i and (i - j < window or j < keep_first)
 
 
+def attention_core(q, k, v, gate_logits, r1, r2, talk, scale, cap, window, keep):
+    """q [T, H, D], k [T, G, D], v [T, G, V], gate_logits [T, H] (or None) -> [T, H, V].  cap 0: no cap; window None: all."""
+    T, H, _ = q.shape
+    G, V = k.shape[1], v.shape[2]
+    window = T + 1 if window is None else window
+    weights = np.zeros((H, T, T))
+    for hd in range(H):
+        g = hd // (H // G)
+        s = q[:, hd] @ k[:, g].T * scale
+        if cap:
+            s = cap * np.tanh(s / cap)
+        for i in range(T):
+            js = [j for j in range(i + 1) if visible(i, j, window, keep)]
+            row = np.array([s[i, j] - r1[hd] * np.log1p(r2[hd] * (i - j)) for j in js])
+            e = np.exp(row - row.max())
+            weights[hd, i, js] = e / e.sum()
+    mixed = np.einsum("hg,gij->hij", talk, weights)
+    out = np.zeros((T, H, V))
+    for hd in range(H):
+        out[:, hd] = mixed[hd] @ v[:, hd // (H // G)]
+    if gate_logits is not None:
+        out = out * sigmoid(gate_logits)[:, :, None]
+    return out
+
+
 def window_attention(h, W, p, m):
     """Softmax attention with grouped key/value heads and no rotation: score = softcap * tanh(q.k * scale / softcap)
     - r1 * ln(1 + r2 * (i - j)); sliding window plus the first ``keep_first`` tokens; the heads' softmax weights are mixed
@@ -89,26 +114,23 @@ def window_attention(h, W, p, m):
     q = (h @ W[p + "q"].T).reshape(T, H, D)
     k = (h @ W[p + "k"].T).reshape(T, G, D)
     v = (h @ W[p + "v"].T).reshape(T, G, V)
-    gate = sigmoid(h @ W[p + "g"].T)                        # [T, H]
-    cap = m["softcap"]
-    window, keep = m["mask"]["size"], m["mask"].get("keep_first", 0)
-    r1, r2 = W[p + "r1"], W[p + "r2"]
-    weights = np.zeros((H, T, T))
-    for hd in range(H):
-        g = hd // (H // G)
-        s = q[:, hd] @ k[:, g].T * m["scale"]
-        s = cap * np.tanh(s / cap)
-        for i in range(T):
-            js = [j for j in range(i + 1) if visible(i, j, window, keep)]
-            row = np.array([s[i, j] - r1[hd] * np.log1p(r2[hd] * (i - j)) for j in js])
-            e = np.exp(row - row.max())
-            weights[hd, i, js] = e / e.sum()
-    mixed = np.einsum("hg,gij->hij", W[p + "talk"], weights)
-    out = np.zeros((T, H, V))
-    for hd in range(H):
-        out[:, hd] = mixed[hd] @ v[:, hd // (H // G)]
-    out = out * gate[:, :, None]
+    mask = m.get("mask") or {}
+    out = attention_core(q, k, v, h @ W[p + "g"].T, W[p + "r1"], W[p + "r2"], W[p + "talk"], m["scale"], m.get("softcap") or 0.0,
+                         mask.get("size"), mask.get("keep_first") or 0)
     return out.reshape(T, H * V) @ W[p + "o"].T
+
+
+def linear_recurrence(q, k, v, a, kscale=None, skip=None, qscale=1.0):
+    """S_t = diag(a_t) S_(t-1) + (kscale_t k_t) v_t^T;  y_t = qscale S_t^T q_t + skip * v_t.
+    q, k [T, n]; v [T, p]; a [T, n] or [T] (one decay for all rows); kscale [T] or None; skip a number or None."""
+    T, n = k.shape
+    S = np.zeros((n, v.shape[1]))
+    y = np.zeros((T, v.shape[1]))
+    for t in range(T):
+        at = a[t] if np.ndim(a[t]) else np.full(n, a[t])
+        S = at[:, None] * S + np.outer(k[t] * (1.0 if kscale is None else kscale[t]), v[t])
+        y[t] = qscale * (S.T @ q[t]) + (0.0 if skip is None else skip * v[t])
+    return y
 
 
 def gated_linear_attention(h, W, p, m, eps):

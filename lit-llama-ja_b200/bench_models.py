@@ -1,5 +1,6 @@
-"""Throughput of a model family beside LLaMA at equal size (``bench.py --family lepalorn``): prefill tokens/s, batch-1 decode
-tokens/s, and the hot kernels of each timed alone against the measured roofline.  Random weights, layer shapes of real
+"""Throughput of a model family beside its closest relative at equal size: prefill tokens/s, batch-1 decode tokens/s, and
+the hot kernels of each timed alone against the measured roofline.  ``bench.py --family lepalorn``: Lepalorn beside LLaMA;
+``bench.py --family bededra``: Bededra beside Lepalorn.  Random weights, layer shapes of real
 models, a few layers each (every layer costs the same).  Timing: CUDA events, warm-up, an L2 flush (a 256 MB write)
 between timed iterations."""
 from __future__ import annotations
@@ -206,9 +207,172 @@ def kernel_table(s, lep, device, timer, prompt_len):
     return rows, which
 
 
+# Bededra at the widths of SIZES: layers alternate parallel / mamba2; left = window attention (kv heads = heads / 4), right =
+# gated linear attention, state space with inner size 2 * width; experts as Lepalorn's at that width (no shared expert)
+BEDEDRA_SIZES = {
+    "w1024": dict(width=1024, layers=4, heads=8, kv=2, dim=64, window=512, keep=16, r_heads=4, r_dim=64, r_vdim=128, rank=16,
+                  m_heads=32, m_vdim=64, state=128, experts=16, top=2, ff=768, groups=4, keep_groups=2),
+    "w2048": dict(width=2048, layers=4, heads=16, kv=4, dim=128, window=1024, keep=16, r_heads=8, r_dim=64, r_vdim=128, rank=16,
+                  m_heads=64, m_vdim=64, state=128, experts=32, top=4, ff=1024, groups=8, keep_groups=4),
+    "w4096": dict(width=4096, layers=2, heads=32, kv=8, dim=128, window=2048, keep=16, r_heads=16, r_dim=64, r_vdim=128, rank=16,
+                  m_heads=128, m_vdim=64, state=128, experts=32, top=4, ff=2048, groups=8, keep_groups=4),
+}
+
+
+def bededra_model(s, device, dtype=torch.bfloat16):
+    from lit_llama.bededra import Bededra, BededraConfig
+
+    ff = {"kind": "moe", "expert": {"ff": s["ff"]},
+          "router": {"experts": s["experts"], "top": s["top"], "groups": {"count": s["groups"], "keep": s["keep_groups"]}}}
+    par = {"type": "parallel", "mlp": ff, "mixer": {
+        "left": {"heads": s["heads"], "kv_heads": s["kv"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5, "softcap": 30.0,
+                 "mask": {"size": s["window"], "keep_first": s["keep"]}},
+        "right": {"heads": s["r_heads"], "dim": s["r_dim"], "vdim": s["r_vdim"], "tau": 8.0, "decay_rank": s["rank"]},
+        "left_scale": 0.7, "right_scale": 1.2}}
+    mam = {"type": "mamba2", "mlp": ff, "mixer": {"heads": s["m_heads"], "vdim": s["m_vdim"], "state": s["state"], "groups": 1,
+                                                  "norm_groups": 1, "conv": 4}}
+    cfg = {"vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-5}, "canon": {"taps": 4},
+           "layers": [par if i % 2 == 0 else mam for i in range(s["layers"])]}
+    m = Bededra(BededraConfig.from_dict(cfg), dtype=dtype, device=device)
+    g = torch.Generator(device=device).manual_seed(0)
+    fixed = {"r1": 0.1, "r2": 1.0, "dt_bias": -1.0, "a_log": 0.0, "skip": 1.0, "b_a2": 2.0}
+    for n, p in m.named_parameters():
+        leaf = n.rsplit(".", 1)[-1]
+        if leaf == "talk":
+            p.copy_(torch.eye(p.shape[0], device=device) + 0.05 * torch.randn(p.shape, generator=g, device=device))
+        elif p.dim() >= 2 and "conv" not in n and "canon" not in n:
+            p.copy_((torch.randn(p.shape, generator=g, device=device) / math.sqrt(p.shape[-1])).to(p.dtype))
+        elif p.dim() >= 2:
+            p.copy_(0.3 * torch.randn(p.shape, generator=g, device=device))
+        elif leaf in fixed:
+            p.fill_(fixed[leaf])
+    return m.eval()
+
+
+def bededra_kernel_table(s, model, device, timer, prompt_len):
+    """The mixers' kernels of one parallel and one mamba2 layer alone.  Roofline time = max(flops / tensor peak, bytes /
+    copy bandwidth), flops and bytes counted for the mechanism (one sweep over the visible keys; one update and one
+    read-out of the state per token), not for what the kernel happens to do."""
+    from torch.nn import functional as F
+
+    from lit_llama import _native as N
+    from lit_llama.recurrence import decay_scan
+
+    hbm, tflops, which = peaks()
+    bf = torch.bfloat16
+    rows = []
+
+    def add(name, t, flops, nbytes):
+        roof = max(flops / tflops, nbytes / hbm)
+        rows.append(dict(kernel=name, us=round(t * 1e6, 1), roofline_us=round(roof * 1e6, 2), fraction=round(roof / t, 4)))
+
+    par = next(b for b in model.blocks if b.kind == "parallel")
+    mam = next(b for b in model.blocks if b.kind == "mamba2")
+    E, H, G, D, W, K = s["width"], s["heads"], s["kv"], s["dim"], s["window"], s["keep"]
+    for T, tag in ((prompt_len, "prefill"), (1, "decode")):
+        pos0 = 0 if T > 1 else prompt_len
+        pos_ids = torch.arange(pos0, pos0 + T, dtype=torch.int32, device=device)
+        model.reset_cache()
+        model._begin(1, prompt_len + 64, True)
+        for t in model.kv_caches:
+            t.normal_()
+        for t in model.states:
+            t.zero_()
+        x = torch.randn((T, E), device=device, dtype=bf)
+        proj = F.linear(x, par.mix.w_in)
+        att = par.mix.left
+        caches = model.kv_caches[:2]
+        span = min(W, caches[0].shape[1] - K) + K
+        splits = 1 if T > 1 else max(1, min(16, (span + 63) // 64))
+        keys = sum(min(W, p + 1) + max(0, min(K, p + 1 - W)) for p in range(pos0, pos0 + T))
+
+        def attn():
+            att.attend(proj, 0, 1, T, pos_ids, caches, splits)
+
+        add(f"window_attn {tag} (append + two sweeps + gate)", timer(attn, graph=True), 2.0 * keys * H * 2 * D,
+            2.0 * (min(W + K + T, pos0 + T) * G * 2 * D + 2 * T * H * D))
+        # gated linear attention: the recurrence alone
+        r = par.mix.right
+        rs = r.spec
+        alpha = torch.rand((T, rs.heads * rs.dim), device=device) * 0.1 + 0.9
+        st_r = model.states[1:2]
+        c0 = par.mix.right_col0
+
+        def gla():
+            decay_scan(proj, c0 + r.cols["q"], proj, c0 + r.cols["k"], proj, c0 + r.cols["v"], alpha, True, None, None, 0.125, st_r[0],
+                       pos_ids, 1, T, rs.heads, rs.heads, rs.dim, rs.vdim)
+
+        nst = rs.heads * rs.dim * rs.vdim
+        add(f"decay_scan {tag} (gated linear attention)", timer(gla, graph=True), 4.0 * T * nst,
+            2.0 * T * rs.heads * (2 * rs.dim + rs.vdim) + 4.0 * T * rs.heads * (rs.dim + rs.vdim) + 8.0 * nst)
+        # state space: the recurrence alone
+        ms = mam.mix.spec
+        xbc = torch.randn((T, ms.conv_channels), device=device, dtype=bf)
+        dtv = torch.rand((T, ms.heads), device=device) * 0.5
+        dec = torch.rand((T, ms.heads), device=device) * 0.1 + 0.9
+        st_m = torch.zeros((1, ms.heads, ms.state, ms.vdim), device=device)
+        gn = ms.groups * ms.state
+
+        def ssm():
+            decay_scan(xbc, ms.inner + gn, xbc, ms.inner, xbc, 0, dec, False, dtv, mam.mix.skip, 1.0, st_m, pos_ids, 1, T, ms.heads,
+                       ms.groups, ms.state, ms.vdim)
+
+        nst = ms.heads * ms.state * ms.vdim
+        add(f"decay_scan {tag} (state space)", timer(ssm, graph=True), 4.0 * T * nst,
+            2.0 * T * ms.conv_channels + 4.0 * T * (2 * ms.heads + ms.inner) + 8.0 * nst)
+        # the layer's short convolution and its two norms (bandwidth)
+        xs = torch.randn((T, E), device=device)
+        h1, h2 = torch.empty((T, E), device=device), torch.empty((T, E), device=device, dtype=bf)
+        from lit_llama.bededra import add_norm_pair
+
+        a0 = torch.randn((T, E), device=device, dtype=bf)
+        add(f"add + two norms {tag}", timer(lambda: add_norm_pair(xs, [(a0, 1.0), (a0, 0.5)], par.norm1, par.norm2, 1e-5, h1, h2, bf),
+                                           graph=True), 0.0, T * E * (4 + 4 + 2 + 2 + 4 + 2))
+        cst = model.states[0]
+        add(f"short_conv {tag}", timer(lambda: par.canon(h1, 0, cst, pos_ids, 1, T, bf, residual=True), graph=True), 0.0, T * E * (4 + 2))
+    return rows, which
+
+
+def run_bededra(args):
+    import sys
+
+    sys.path.insert(0, str(ROOT))
+    from __graft_entry__ import build
+
+    build()
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    timer = Timer(device)
+    prompt_len = 2048
+    out = {"family": "bededra", "beside": "lepalorn", "dtype": "bf16", "data": "synthetic (random weights)", "prompt_len": prompt_len,
+           "batch": 1, "l2": "256 MB written between timed iterations", "sizes": {}}
+    names = [n for n in BEDEDRA_SIZES if not getattr(args, "size", None) or n == args.size]
+    for name in names:
+        s = BEDEDRA_SIZES[name]
+        with torch.no_grad():
+            m = bededra_model(s, device)
+            pre, dec = end_to_end(m, timer, prompt_len, device, prompt_len + 64)
+            rows, which = bededra_kernel_table(s, m, device, timer, prompt_len)
+            del m
+            torch.cuda.empty_cache()
+            lep = lepalorn_model(SIZES[name], device)
+            lpre, ldec = end_to_end(lep, timer, prompt_len, device, prompt_len + 64)
+            lrows, _ = kernel_table(SIZES[name], lep, device, timer, prompt_len)
+            del lep
+            torch.cuda.empty_cache()
+        out["sizes"][name] = {"config": s, "bededra": {"prefill_tokens_per_s": round(pre), "decode_tokens_per_s": round(dec, 1)},
+                              "lepalorn_same_width": {"prefill_tokens_per_s": round(lpre), "decode_tokens_per_s": round(ldec, 1)},
+                              "kernels": rows, "lepalorn_kernels": [r for r in lrows if not r["kernel"].startswith("llama")],
+                              "roofline": f"of {which}"}
+    print(json.dumps(out))
+    return 0
+
+
 def run(args):
     import sys
 
+    if args.family == "bededra":
+        return run_bededra(args)
     sys.path.insert(0, str(ROOT))
     from __graft_entry__ import build
 

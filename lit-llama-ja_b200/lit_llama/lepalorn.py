@@ -8,14 +8,13 @@ average over the outputs of all earlier layers (depth-weighted average) after ev
     logits = head (g_f * rmsnorm(x))
 
 The residual stream, the X_j, the norms, rotary angles, attention scores and router logits are fp32 whatever the dtype of
-the GEMMs.  ``forward(idx, max_seq_length, input_pos)`` has LLaMA's signature (model.py), so ``generate()`` drives both;
-per-token state lives in ring tensors from the package's ``TensorPool`` (cache.py) and is written in place.
-Single-token steps replay one CUDA graph per (batch, ring length).
+the GEMMs.  ``forward`` is the package's common step function (stepping.PortionedDecoder: LLaMA's signature, prompts in passes,
+single-token steps as one CUDA graph per (batch, ring length)); per-token state lives in ring tensors from the package's
+``TensorPool`` (cache.py) and is written in place.
 """
 from __future__ import annotations
 
 import json
-import os
 from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Dict, List, Optional, Tuple
@@ -27,6 +26,7 @@ from . import _native as N
 from .cache import TensorPool, max_portion, ring_length
 from .latent_attention import LatentAttention, LatentAttentionSpec, build_rope_table
 from .moe import MoE, MoESpec
+from .stepping import PortionedDecoder, head_logits
 
 ARCHITECTURE = "Lepalorn"
 
@@ -145,12 +145,8 @@ class LepalornBlock(nn.Module):
         self.dwa.copy_(get(p + "dwa").float())
 
 
-class Lepalorn(nn.Module):
+class Lepalorn(PortionedDecoder):
     architecture = ARCHITECTURE
-    use_fused_decode = False       # generate(): the per-op sampling loop drives this model
-    use_step_graph = True          # single-token steps replay one CUDA graph per (batch, ring length)
-    prefill_portion = 4096         # most tokens one pass appends; longer prompts run as several passes
-    layer_probe = None             # callable(layer index, fp32 stream [B*T, width]) after every layer, for inspection
 
     def __init__(self, config: LepalornConfig, dtype: torch.dtype = torch.bfloat16, device="cuda") -> None:
         super().__init__()
@@ -166,7 +162,6 @@ class Lepalorn(nn.Module):
         self._pool = TensorPool(max_sets=2, on_evict=self._drop_graphs)
         self._rope: Dict[Tuple[float, int], torch.Tensor] = {}
         self._rope_len = 0
-        self._step_graphs: Dict[tuple, dict] = {}
         self.kv_caches: List[torch.Tensor] = []       # one ring per layer that owns a cache (index: _cache_of[layer])
         self._ring = 0
         self._cache_of: List[int] = []
@@ -207,9 +202,6 @@ class Lepalorn(nn.Module):
         return model.eval()
 
     # ------------------------------------------------------------------ cache
-    def _drop_graphs(self) -> None:
-        self._step_graphs.clear()
-
     def reset_cache(self) -> None:
         """The sequences end: their rows are given back (the rings stay allocated and are written over from position 0)."""
         self.kv_caches = []
@@ -236,70 +228,24 @@ class Lepalorn(nn.Module):
         self._rope_len = n
         self._drop_graphs()
 
-    # ------------------------------------------------------------------ forward
-    @torch.no_grad()
-    def forward(self, idx: torch.Tensor, max_seq_length: Optional[int] = None, input_pos: Optional[torch.Tensor] = None,
-                out_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """``idx [B, T]`` at positions ``input_pos [T]`` (consecutive; None: a forward without a kept cache from position 0).
-        Returns fp32 logits ``[B, T, vocab]``, or ``[B, len(out_rows), vocab]`` for the token indices in ``out_rows``."""
-        N.require_cuda(idx)
-        B, T = idx.shape
-        keep = input_pos is not None
-        if not keep:
-            saved = (self.kv_caches, self._ring)
-            self.kv_caches, pos0 = [], 0
-            max_seq_length = T
-        else:
-            pos0 = int(input_pos[0])
-            if max_seq_length is None:
-                max_seq_length = max(pos0 + T, self._ring)
-        assert pos0 + T <= max_seq_length, f"positions up to {pos0 + T} but the cache holds {max_seq_length}"
+    # ------------------------------------------------------------------ hooks of the common step function (stepping.py)
+    def _begin(self, B: int, max_seq_length: int, keep: bool) -> None:
         self._ensure_cache(B, max_seq_length, pooled=keep)
         self._ensure_rope(max_seq_length)
-        piece = min(self.prefill_portion, min(max_portion(self._ring, max_seq_length, w) for w in self._windows))
-        rows = None if out_rows is None else [int(r) for r in out_rows]
-        outs = []
-        for t0 in range(0, T, piece):
-            t1 = min(T, t0 + piece)
-            sel = None
-            if rows is not None:
-                sel = [r - t0 for r in rows if t0 <= r < t1]
-            part = idx[:, t0:t1]
-            if t1 - t0 == 1 and keep and self.use_step_graph and os.environ.get("LLB200_STEP_GRAPH", "1") != "0" \
-                    and not torch.cuda.is_current_stream_capturing():
-                lg = self._graphed_step(part, pos0 + t0)
-                if sel is not None:
-                    lg = lg[:, sel]
-            else:
-                pos_ids = torch.arange(pos0 + t0, pos0 + t1, dtype=torch.int32, device=idx.device)
-                lg = self._forward_portion(part.contiguous(), pos_ids, sel)
-            outs.append(lg)
-        if not keep:
-            self.kv_caches, self._ring = saved
-        return outs[0] if len(outs) == 1 else torch.cat(outs, dim=1)
 
-    def _graphed_step(self, idx: torch.Tensor, pos: int) -> torch.Tensor:
-        B = idx.shape[0]
-        key = (B, self._ring, self.kv_caches[0].data_ptr())
-        ent = self._step_graphs.get(key)
-        if ent is None:
-            s_idx = idx.clone()
-            s_pos = torch.full((1,), pos, dtype=torch.int32, device=idx.device)
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):          # warm-up: library handles and workspaces (rewrites this step's own cache row)
-                for _ in range(2):
-                    self._forward_portion(s_idx, s_pos, None)
-            torch.cuda.current_stream().wait_stream(side)
-            torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                out = self._forward_portion(s_idx, s_pos, None)
-            ent = self._step_graphs[key] = dict(graph=g, idx=s_idx, pos=s_pos, out=out)
-        ent["idx"].copy_(idx)
-        ent["pos"].fill_(pos)
-        ent["graph"].replay()
-        return ent["out"].clone()
+    def _piece(self, max_seq_length: int) -> int:
+        return min(max_portion(self._ring, max_seq_length, w) for w in self._windows)
+
+    def _graph_key(self, B: int) -> tuple:
+        return (B, self._ring, self.kv_caches[0].data_ptr())
+
+    def _save_memory(self):
+        saved = (self.kv_caches, self._ring)
+        self.kv_caches = []
+        return saved
+
+    def _restore_memory(self, saved) -> None:
+        self.kv_caches, self._ring = saved
 
     def _forward_portion(self, idx: torch.Tensor, pos_ids: torch.Tensor, sel) -> torch.Tensor:
         cfg = self.config
@@ -342,11 +288,4 @@ class Lepalorn(nn.Module):
             x = x.index_select(0, ridx).contiguous()
         xn = torch.empty((x.shape[0], E), dtype=self.dtype, device=dev)
         gain_norm_add_mix(None, x, self.final_norm, cfg.eps, nxt_act=xn)
-        if self.dtype == torch.float32:
-            logits = xn @ self.head.t()
-        else:
-            try:
-                logits = torch.mm(xn, self.head.t(), out_dtype=torch.float32)
-            except RuntimeError:           # a width the library's mixed-output GEMM does not take: fp32 product of the same operands
-                logits = xn.float() @ self.head.float().t()
-        return logits[:, : cfg.vocab].reshape(B, -1, cfg.vocab)
+        return head_logits(xn, self.head, cfg.vocab).reshape(B, -1, cfg.vocab)

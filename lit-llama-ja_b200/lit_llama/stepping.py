@@ -26,6 +26,7 @@ class PortionedDecoder(nn.Module):
     def __init__(self) -> None:
         super().__init__()
         self._step_graphs: Dict[tuple, dict] = {}
+        self._sized_for = 0
 
     # ------------------------------------------------------------------ hooks
     def _begin(self, B: int, max_seq_length: int, keep: bool) -> None:
@@ -68,8 +69,9 @@ class PortionedDecoder(nn.Module):
             pos0, max_seq_length = 0, T
         else:
             pos0 = int(input_pos[0])
-            if max_seq_length is None:
-                max_seq_length = pos0 + T
+            if max_seq_length is None:         # the length the memory was last sized for, unless the sequence outgrows it
+                max_seq_length = max(pos0 + T, self._sized_for)
+            self._sized_for = max_seq_length
         assert pos0 + T <= max_seq_length, f"positions up to {pos0 + T} but the cache holds {max_seq_length}"
         self._begin(B, max_seq_length, keep)
         piece = max(1, min(self.prefill_portion, self._piece(max_seq_length)))

@@ -77,8 +77,11 @@ class WindowAttention(nn.Module):
         self.w_o.copy_(get("o"))
 
     def forward(self, proj: torch.Tensor, col0: int, B: int, T: int, pos_ids: torch.Tensor, caches, splits: int = 1) -> torch.Tensor:
+        return F.linear(self.attend(proj, col0, B, T, pos_ids, caches, splits), self.w_o)
+
+    def attend(self, proj: torch.Tensor, col0: int, B: int, T: int, pos_ids: torch.Tensor, caches, splits: int = 1) -> torch.Tensor:
         """``proj``: the stacked input projection's output, this mixer's columns starting at ``col0``; ``caches`` = (keys,
-        values), appended to here."""
+        values), appended to here.  Returns the gated heads ``[B*T, heads * vdim]`` (before the output projection)."""
         s = self.spec
         c = self.cols
         kc, vc = caches
@@ -95,4 +98,4 @@ class WindowAttention(nn.Module):
                N.ptr(vc), dtc, N.ptr(pos_ids), N.ptr(self.r1), N.ptr(self.r2), N.ptr(self.talk), float(s.scale), float(s.softcap), B, T,
                s.heads, s.kv_heads, s.dim, s.vdim, s.window if s.window is not None else UNBOUNDED, s.keep_first, ring, splits,
                N.ptr(scratch), N.ptr(y), st)
-        return F.linear(y, self.w_o)
+        return y

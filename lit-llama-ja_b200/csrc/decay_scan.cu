@@ -18,7 +18,8 @@ constexpr int DS_NL = 16;       // state rows a thread keeps in registers
 __host__ __device__ constexpr int ds_tc(int np) { return np <= 8 ? 16 : 4; }
 
 // grid (p tiles, H, B).  NP threads (consecutive lanes) share one column c and split the n rows; PT = DS_THREADS / NP
-// columns per block.
+// columns per block.  A thread's rows are interleaved in quads, row(k, e) = (k * NP + part) * 4 + e, so that the NP lanes of
+// a column read consecutive 16-byte units of the staged token (no bank conflicts).
 template <typename T, int NP>
 __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
     const T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride, const T* __restrict__ v, int v_stride,
@@ -35,52 +36,75 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
   const int part = threadIdx.x % NP, pl = threadIdx.x / NP;
   const int c = blockIdx.x * PT + pl;
   const bool live = c < p;
-  const int i0 = part * DS_NL;
   float S[DS_NL];
+#define DS_ROW(i) ((((i) >> 2) * NP + part) * 4 + ((i) & 3))
   float* sp = state + (((size_t)b * H + h) * n) * p;
   const bool fresh = pos_ids[0] == 0;
 #pragma unroll
-  for (int i = 0; i < DS_NL; ++i) S[i] = (!fresh && live && i0 + i < n) ? sp[(size_t)(i0 + i) * p + c] : 0.f;
+  for (int i = 0; i < DS_NL; ++i) S[i] = (!fresh && live && DS_ROW(i) < n) ? sp[(size_t)DS_ROW(i) * p + c] : 0.f;
   const float sk = skip ? skip[h] : 0.f;
-  for (int t0 = 0; t0 < Tn; t0 += DS_TC) {
-    const int nt = min(DS_TC, Tn - t0);
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < nt * NPAD; idx += DS_THREADS) {
+  // The next round's tokens are fetched into registers while this round's are consumed from shared memory.
+  constexpr int IT = DS_TC * NPAD / DS_THREADS, VIT = (DS_TC * PT + DS_THREADS - 1) / DS_THREADS;
+  float ra[IT], rk[IT], rq[IT], rv[VIT];
+  auto fetch = [&](int t0) {
+#pragma unroll
+    for (int it = 0; it < IT; ++it) {
+      const int idx = it * DS_THREADS + threadIdx.x;
       const int tt = idx / NPAD, i = idx - tt * NPAD;
       const size_t m = (size_t)b * Tn + t0 + tt;
       float av = 1.f, kv = 0.f, qv = 0.f;
-      if (i < n) {
+      if (t0 + tt < Tn && i < n) {
         av = a_per_channel ? a[(m * H + h) * n + i] : a[m * H + h];
         kv = dt<T>::ld(k, m * k_stride + (size_t)g * n + i) * (ks ? ks[m * H + h] : 1.f);
         qv = dt<T>::ld(q, m * q_stride + (size_t)g * n + i) * qs;
       }
-      s_a[tt][i] = av;
-      s_k[tt][i] = kv;
-      s_q[tt][i] = qv;
+      ra[it] = av; rk[it] = kv; rq[it] = qv;
     }
-    for (int idx = threadIdx.x; idx < nt * PT; idx += DS_THREADS) {
+#pragma unroll
+    for (int it = 0; it < VIT; ++it) {
+      const int idx = it * DS_THREADS + threadIdx.x;
       const int tt = idx / PT, cc = idx - tt * PT;
       const int col = blockIdx.x * PT + cc;
-      s_v[tt][cc] = col < p ? dt<T>::ld(v, ((size_t)b * Tn + t0 + tt) * v_stride + (size_t)h * p + col) : 0.f;
+      rv[it] = (tt < DS_TC && t0 + tt < Tn && col < p) ? dt<T>::ld(v, ((size_t)b * Tn + t0 + tt) * v_stride + (size_t)h * p + col) : 0.f;
+    }
+  };
+  fetch(0);
+  for (int t0 = 0; t0 < Tn; t0 += DS_TC) {
+    const int nt = min(DS_TC, Tn - t0);
+    __syncthreads();
+#pragma unroll
+    for (int it = 0; it < IT; ++it) {
+      const int idx = it * DS_THREADS + threadIdx.x;
+      const int tt = idx / NPAD, i = idx - tt * NPAD;
+      s_a[tt][i] = ra[it]; s_k[tt][i] = rk[it]; s_q[tt][i] = rq[it];
+    }
+#pragma unroll
+    for (int it = 0; it < VIT; ++it) {
+      const int idx = it * DS_THREADS + threadIdx.x;
+      const int tt = idx / PT, cc = idx - tt * PT;
+      if (tt < DS_TC) s_v[tt][cc] = rv[it];
     }
     __syncthreads();
+    if (t0 + DS_TC < Tn) fetch(t0 + DS_TC);
     for (int tt = 0; tt < nt; ++tt) {
       const float vv = s_v[tt][pl];
-      float acc = 0.f;
+      float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
 #pragma unroll
       for (int i4 = 0; i4 < DS_NL; i4 += 4) {
-        const float4 a4 = *(const float4*)&s_a[tt][i0 + i4];
-        const float4 k4 = *(const float4*)&s_k[tt][i0 + i4];
-        const float4 q4 = *(const float4*)&s_q[tt][i0 + i4];
+        const int at = ((i4 >> 2) * NP + part) * 4;
+        const float4 a4 = *(const float4*)&s_a[tt][at];
+        const float4 k4 = *(const float4*)&s_k[tt][at];
+        const float4 q4 = *(const float4*)&s_q[tt][at];
         S[i4 + 0] = a4.x * S[i4 + 0] + k4.x * vv;
         S[i4 + 1] = a4.y * S[i4 + 1] + k4.y * vv;
         S[i4 + 2] = a4.z * S[i4 + 2] + k4.z * vv;
         S[i4 + 3] = a4.w * S[i4 + 3] + k4.w * vv;
-        acc += q4.x * S[i4 + 0];
-        acc += q4.y * S[i4 + 1];
-        acc += q4.z * S[i4 + 2];
-        acc += q4.w * S[i4 + 3];
+        c0 += q4.x * S[i4 + 0];
+        c1 += q4.y * S[i4 + 1];
+        c2 += q4.z * S[i4 + 2];
+        c3 += q4.w * S[i4 + 3];
       }
+      float acc = (c0 + c1) + (c2 + c3);
 #pragma unroll
       for (int o = NP / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (part == 0 && live) y[((size_t)b * Tn + t0 + tt) * ((size_t)H * p) + (size_t)h * p + c] = acc + sk * vv;
@@ -89,8 +113,9 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
   if (live) {
 #pragma unroll
     for (int i = 0; i < DS_NL; ++i)
-      if (i0 + i < n) sp[(size_t)(i0 + i) * p + c] = S[i];
+      if (DS_ROW(i) < n) sp[(size_t)DS_ROW(i) * p + c] = S[i];
   }
+#undef DS_ROW
 }
 
 template <typename T, int NP>

@@ -196,7 +196,11 @@ def attention_want(att, proj, params, dtype):
 
 
 @pytest.mark.parametrize("H,G,D,V,window,keep", [(4, 2, 8, 8, 6, 2), (3, 3, 5, 7, 4, 0), (6, 1, 16, 4, 9, 3), (1, 1, 4, 4, 1, 0),
-                                                 (2, 2, 8, 12, None, 0), (8, 4, 64, 64, 12, 5), (2, 1, 8, 8, 3, 7)])
+                                                 (2, 2, 8, 12, None, 0), (8, 4, 64, 64, 12, 5), (2, 1, 8, 8, 3, 7),
+                                                 # sizes the tensor-core form takes in bfloat16 (heads padded to 16; two heads
+                                                 # per warp and two rounds of output heads; one head)
+                                                 (3, 1, 16, 16, 5, 1), (16, 4, 32, 16, 20, 3), (32, 8, 16, 32, 9, 2),
+                                                 (1, 1, 128, 128, None, 0), (40, 40, 16, 16, 7, 0)])
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_window_attention_on_a_wrapping_ring(H, G, D, V, window, keep, dtype):
     T = 40

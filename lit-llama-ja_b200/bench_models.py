@@ -283,7 +283,7 @@ def bededra_kernel_table(s, model, device, timer, prompt_len):
         att = par.mix.left
         caches = model.kv_caches[:2]
         span = min(W, caches[0].shape[1] - K) + K
-        splits = 1 if T > 1 else max(1, min(16, (span + 63) // 64))
+        splits = 1 if T > 1 else max(1, min(64, (span + 63) // 64))
         keys = sum(min(W, p + 1) + max(0, min(K, p + 1 - W)) for p in range(pos0, pos0 + T))
 
         def attn():

@@ -15,7 +15,7 @@ namespace llb {
 constexpr int DS_THREADS = 128;
 constexpr int DS_NL = 16;       // state rows a thread keeps in registers
 // tokens staged per round (fewer when a head's state rows are many, so that the staging stays small)
-__host__ __device__ constexpr int ds_tc(int np) { return np <= 8 ? 16 : 4; }
+__host__ __device__ constexpr int ds_tc(int np) { return np <= 4 ? 16 : np == 8 ? 8 : np == 16 ? 4 : 2; }
 
 // grid (p tiles, H, B).  NP threads (consecutive lanes) share one column c and split the n rows; PT = DS_THREADS / NP
 // columns per block.  A thread's rows are interleaved in quads, row(k, e) = (k * NP + part) * 4 + e, so that the NP lanes of
@@ -45,27 +45,28 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
   const float sk = skip ? skip[h] : 0.f;
   // The next round's tokens are fetched into registers while this round's are consumed from shared memory.
   constexpr int IT = DS_TC * NPAD / DS_THREADS, VIT = (DS_TC * PT + DS_THREADS - 1) / DS_THREADS;
-  float ra[IT], rk[IT], rq[IT], rv[VIT];
+  // (raw values only: nothing may depend on a load before the round that consumes it, or the fetch would wait for it)
+  float ra[IT], rs[IT];
+  T rk[IT], rq[IT], rv[VIT];
   auto fetch = [&](int t0) {
 #pragma unroll
     for (int it = 0; it < IT; ++it) {
       const int idx = it * DS_THREADS + threadIdx.x;
       const int tt = idx / NPAD, i = idx - tt * NPAD;
       const size_t m = (size_t)b * Tn + t0 + tt;
-      float av = 1.f, kv = 0.f, qv = 0.f;
-      if (t0 + tt < Tn && i < n) {
-        av = a_per_channel ? a[(m * H + h) * n + i] : a[m * H + h];
-        kv = dt<T>::ld(k, m * k_stride + (size_t)g * n + i) * (ks ? ks[m * H + h] : 1.f);
-        qv = dt<T>::ld(q, m * q_stride + (size_t)g * n + i) * qs;
-      }
-      ra[it] = av; rk[it] = kv; rq[it] = qv;
+      const bool ok = t0 + tt < Tn && i < n;
+      ra[it] = ok ? (a_per_channel ? a[(m * H + h) * n + i] : a[m * H + h]) : 1.f;
+      rs[it] = (ok && ks) ? ks[m * H + h] : 1.f;
+      rk[it] = k[ok ? m * k_stride + (size_t)g * n + i : 0];
+      rq[it] = q[ok ? m * q_stride + (size_t)g * n + i : 0];
     }
 #pragma unroll
     for (int it = 0; it < VIT; ++it) {
       const int idx = it * DS_THREADS + threadIdx.x;
       const int tt = idx / PT, cc = idx - tt * PT;
       const int col = blockIdx.x * PT + cc;
-      rv[it] = (tt < DS_TC && t0 + tt < Tn && col < p) ? dt<T>::ld(v, ((size_t)b * Tn + t0 + tt) * v_stride + (size_t)h * p + col) : 0.f;
+      const bool ok = tt < DS_TC && t0 + tt < Tn && col < p;
+      rv[it] = v[ok ? ((size_t)b * Tn + t0 + tt) * v_stride + (size_t)h * p + col : 0];
     }
   };
   fetch(0);
@@ -76,13 +77,16 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
     for (int it = 0; it < IT; ++it) {
       const int idx = it * DS_THREADS + threadIdx.x;
       const int tt = idx / NPAD, i = idx - tt * NPAD;
-      s_a[tt][i] = ra[it]; s_k[tt][i] = rk[it]; s_q[tt][i] = rq[it];
+      const bool ok = t0 + tt < Tn && i < n;
+      s_a[tt][i] = ra[it];
+      s_k[tt][i] = ok ? dt<T>::ld(&rk[it], 0) * rs[it] : 0.f;
+      s_q[tt][i] = ok ? dt<T>::ld(&rq[it], 0) * qs : 0.f;
     }
 #pragma unroll
     for (int it = 0; it < VIT; ++it) {
       const int idx = it * DS_THREADS + threadIdx.x;
       const int tt = idx / PT, cc = idx - tt * PT;
-      if (tt < DS_TC) s_v[tt][cc] = rv[it];
+      if (tt < DS_TC) s_v[tt][cc] = (t0 + tt < Tn && blockIdx.x * PT + cc < p) ? dt<T>::ld(&rv[it], 0) : 0.f;
     }
     __syncthreads();
     if (t0 + DS_TC < Tn) fetch(t0 + DS_TC);

@@ -243,18 +243,28 @@ __global__ void __launch_bounds__(WA_THREADS) window_attn_out_kernel(WaParams P)
   }
 }
 
-// y[m][h * vdim + c] = out_scale * sigmoid(gate[m][h]) * sum_s part[s][m][h * vdim + c]
+// y[m][h * vdim + c] = sigmoid(gate[m][h]) * sum_s part[s][m][h * vdim + c]   (the parts summed in split order)
 template <typename T>
 __global__ void window_attn_finish_kernel(const float* __restrict__ part, int splits, const T* __restrict__ gate, int gate_stride,
                                           T* __restrict__ y, int M, int H, int vdim) {
   const int m = blockIdx.x;
   const int HV = H * vdim;
-  for (int i = threadIdx.x; i < HV; i += blockDim.x) {
-    float s = 0.f;
-    for (int k = 0; k < splits; ++k) s += part[((size_t)k * M + m) * HV + i];
-    if (gate) s *= 1.f / (1.f + expf(-dt<T>::ld(gate, (size_t)m * gate_stride + i / vdim)));
-    dt<T>::st(y, (size_t)m * HV + i, s);
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= HV) return;
+  const float* src = part + (size_t)m * HV + i;
+  const size_t step = (size_t)M * HV;
+  float s = 0.f;
+  int k = 0;
+  for (; k + 8 <= splits; k += 8) {          // eight independent loads in flight, added in order
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = src[(size_t)(k + e) * step];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s += v[e];
   }
+  for (; k < splits; ++k) s += src[(size_t)k * step];
+  if (gate) s *= 1.f / (1.f + expf(-dt<T>::ld(gate, (size_t)m * gate_stride + i / vdim)));
+  dt<T>::st(y, (size_t)m * HV + i, s);
 }
 
 // Append the step's key and value rows (column slices of projection outputs) to the kept-tokens + ring cache.
@@ -614,7 +624,8 @@ static int window_attn_run(WaParams& P, const void* gate, int gate_stride, void*
     if (P.H <= 2 * WM_WARPS) return wm_launch<2>(P, gate, gate_stride, y, smem, st);
     return wm_launch<4>(P, gate, gate_stride, y, smem, st);
   }
-  wa_layout(P, 96 * 1024, &smem);
+  // many queries: two blocks per SM; few (decoding): one chunk as long as shared memory allows, one per split if possible
+  wa_layout(P, (size_t)P.B * P.T * P.splits <= 2 * (size_t)sm_count() ? 200 * 1024 : 96 * 1024, &smem);
   if (smem > 220 * 1024) {
     set_error("window_attn: %d heads of %d do not fit shared memory", P.H, P.dim);
     return LL_ERR_UNSUPPORTED;
@@ -631,7 +642,8 @@ static int window_attn_run(WaParams& P, const void* gate, int gate_stride, void*
   LL_LAUNCH_OK("window_attn_stats_kernel");
   window_attn_out_kernel<T><<<grid, WA_THREADS, smem, st>>>(P);
   LL_LAUNCH_OK("window_attn_out_kernel");
-  window_attn_finish_kernel<T><<<M, 256, 0, st>>>(P.part, P.splits, (const T*)gate, gate_stride, (T*)y, M, P.H, P.vdim);
+  window_attn_finish_kernel<T><<<dim3(M, (P.H * P.vdim + 127) / 128), 128, 0, st>>>(P.part, P.splits, (const T*)gate, gate_stride, (T*)y, M,
+                                                                                     P.H, P.vdim);
   LL_LAUNCH_OK("window_attn_finish_kernel");
   return LL_OK;
 }

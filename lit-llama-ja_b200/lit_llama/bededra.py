@@ -331,7 +331,7 @@ class Bededra(PortionedDecoder):
             else:
                 spec = blk.mix.left.spec
                 span = min(spec.window if spec.window is not None else (1 << 30), self._rings[ci // 2]) + spec.keep_first
-                splits = max(1, min(16, (2 * sms) // max(1, M), (span + 63) // 64))     # few queries: share a long window among blocks
+                splits = max(1, min(64, (2 * sms) // max(1, M), (span + 63) // 64))     # few queries: share a long window among blocks
                 pending = blk.mix(u, B, T, pos_ids, self.kv_caches[ci:ci + 2], self.states[si:si + 1], splits)
                 ci += 2
                 si += 1

@@ -13,14 +13,14 @@
 namespace llb {
 
 constexpr int DS_THREADS = 128;
-constexpr int DS_NL = 16;       // state rows a thread keeps in registers
 // tokens staged per round (fewer when a head's state rows are many, so that the staging stays small)
-__host__ __device__ constexpr int ds_tc(int np) { return np <= 4 ? 16 : np == 8 ? 8 : np == 16 ? 4 : 2; }
+__host__ __device__ constexpr int ds_tc(int npad) { return npad <= 64 ? 16 : npad <= 128 ? 8 : npad <= 256 ? 4 : 2; }
 
 // grid (p tiles, H, B).  NP threads (consecutive lanes) share one column c and split the n rows; PT = DS_THREADS / NP
 // columns per block.  A thread's rows are interleaved in quads, row(k, e) = (k * NP + part) * 4 + e, so that the NP lanes of
 // a column read consecutive 16-byte units of the staged token (no bank conflicts).
-template <typename T, int NP>
+// DS_NL: state rows a thread keeps in registers (8: more threads per head, the usual case; 16: heads of more than 256 rows).
+template <typename T, int NP, int DS_NL>
 __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
     const T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride, const T* __restrict__ v, int v_stride,
     const float* __restrict__ a, int a_per_channel, const float* __restrict__ ks, const float* __restrict__ skip, float qs,
@@ -28,7 +28,7 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
     int p) {
   constexpr int PT = DS_THREADS / NP;
   constexpr int NPAD = NP * DS_NL;
-  constexpr int DS_TC = ds_tc(NP);
+  constexpr int DS_TC = ds_tc(NPAD);
   __shared__ __align__(16) float s_a[DS_TC][NPAD], s_k[DS_TC][NPAD], s_q[DS_TC][NPAD];
   __shared__ float s_v[DS_TC][PT];
   const int h = blockIdx.y, b = blockIdx.z;
@@ -90,6 +90,8 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
     }
     __syncthreads();
     if (t0 + DS_TC < Tn) fetch(t0 + DS_TC);
+    // unrolled so that a token's shared-memory reads run under the previous token's arithmetic
+#pragma unroll 4
     for (int tt = 0; tt < nt; ++tt) {
       const float vv = s_v[tt][pl];
       float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
@@ -122,12 +124,12 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
 #undef DS_ROW
 }
 
-template <typename T, int NP>
+template <typename T, int NP, int NL>
 static int decay_scan_launch(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, const float* a,
                              int a_per_channel, const float* ks, const float* skip, float qs, float* state, const int32_t* pos_ids,
                              float* y, int B, int Tn, int H, int qk_heads, int n, int p, cudaStream_t st) {
   constexpr int PT = DS_THREADS / NP;
-  decay_scan_kernel<T, NP><<<dim3((p + PT - 1) / PT, H, B), DS_THREADS, 0, st>>>((const T*)q, q_stride, (const T*)k, k_stride,
+  decay_scan_kernel<T, NP, NL><<<dim3((p + PT - 1) / PT, H, B), DS_THREADS, 0, st>>>((const T*)q, q_stride, (const T*)k, k_stride,
                                                                                 (const T*)v, v_stride, a, a_per_channel, ks, skip,
                                                                                 qs, state, pos_ids, y, Tn, H, qk_heads, n, p);
   LL_LAUNCH_OK("decay_scan_kernel");
@@ -174,17 +176,25 @@ int ll_decay_scan(const void* q, int q_stride, const void* k, int k_stride, cons
                   int B, int T, int H, int qk_heads, int n, int p, ll_stream stream) {
   LL_CHECK_ARG(q && k && v && a && state && pos_ids && y, "decay_scan: null pointer");
   LL_CHECK_ARG(B >= 0 && T >= 0 && H > 0 && qk_heads > 0 && H % qk_heads == 0 && n > 0 && p > 0, "bad decay_scan arguments");
-  if (n > 32 * DS_NL) {
-    set_error("decay_scan: %d state rows per head (up to %d)", n, 32 * DS_NL);
+  if (n > 32 * 16) {
+    set_error("decay_scan: %d state rows per head (up to %d)", n, 32 * 16);
     return LL_ERR_UNSUPPORTED;
   }
   if (B == 0 || T == 0) return LL_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  // 16 rows per thread when that already gives half of the SMs a block (each block stages its head's tokens: fewer blocks,
+  // less staging); 8 rows when the heads are few, so that twice as many warps share the latency of the sequential walk
+  int np16 = 1;
+  while (np16 * 16 < n) np16 *= 2;
+  const long long blocks16 = (long long)B * H * ((p + DS_THREADS / np16 - 1) / (DS_THREADS / np16));
+  const int nl = (n > 256 || 2 * blocks16 >= sm_count()) ? 16 : 8;
   int np = 1;
-  while (np * DS_NL < n) np *= 2;
-#define LL_DS(TT, NP)                                                                                                            \
-  return decay_scan_launch<TT, NP>(q, q_stride, k, k_stride, v, v_stride, a, a_per_channel, ks, skip, qs, state, pos_ids, y, B, T, \
-                                   H, qk_heads, n, p, st)
+  while (np * nl < n) np *= 2;
+#define LL_DS(TT, NP)                                                                                                                 \
+  return nl == 8 ? decay_scan_launch<TT, NP, 8>(q, q_stride, k, k_stride, v, v_stride, a, a_per_channel, ks, skip, qs, state, pos_ids, \
+                                                y, B, T, H, qk_heads, n, p, st)                                                        \
+                 : decay_scan_launch<TT, NP, 16>(q, q_stride, k, k_stride, v, v_stride, a, a_per_channel, ks, skip, qs, state, pos_ids, \
+                                                 y, B, T, H, qk_heads, n, p, st)
 #define LL_DS_T(TT)                 \
   switch (np) {                     \
     case 1: LL_DS(TT, 1);           \

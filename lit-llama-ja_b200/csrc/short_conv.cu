@@ -44,7 +44,8 @@ __global__ void __launch_bounds__(SC_THREADS) short_conv_kernel(const TX* __rest
     }
     win[j] = v;
   }
-  for (int t = t0; t < t1; ++t) {
+#pragma unroll 8
+  for (int t = t0; t < t1; ++t) {          // unrolled: the loads of eight tokens are in flight together
     const float cur = dt<TX>::ld(xb, (size_t)t * x_stride);
     float acc = bs;
 #pragma unroll
@@ -100,7 +101,7 @@ static int short_conv_launch(const void* x, int x_stride, int col0, const float*
                              cudaStream_t st) {
   // time tiles: enough blocks to fill the device, at least 32 tokens each (every tile re-reads taps-1 inputs)
   const int ctiles = (C + SC_THREADS - 1) / SC_THREADS;
-  int tiles = max(1, min((T + 31) / 32, (4 * sm_count() + ctiles * B - 1) / (ctiles * B)));
+  int tiles = max(1, min((T + 31) / 32, (8 * sm_count() + ctiles * B - 1) / (ctiles * B)));
   const int t_tile = (T + tiles - 1) / tiles;
   tiles = (T + t_tile - 1) / t_tile;
   const int fuse = tiles == 1 && state != nullptr;

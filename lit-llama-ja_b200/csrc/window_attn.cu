@@ -423,8 +423,10 @@ __global__ void __launch_bounds__(WM_THREADS) window_attn_mma_kernel(WaParams P,
   }
   for (int idx = threadIdx.x; idx < Hp * WM_Q * WM_PP; idx += WM_THREADS) Ps[idx] = __float2bfloat16_rn(0.f);   // rows of heads past H stay zero
 
-  uint32_t qf[HPW == 1 ? 1 : 1][WM_DK_MAX][4];
-  if (HPW == 1 && warp < P.H) wm_load_q(P, tl, warp, lane, qf[0]);
+  uint32_t qf[HPW][WM_DK_MAX][4];          // the warp's query fragments stay in registers (spilled where they do not fit)
+#pragma unroll
+  for (int hs = 0; hs < HPW; ++hs)
+    if (warp + hs * WM_WARPS < P.H) wm_load_q(P, tl, warp + hs * WM_WARPS, lane, qf[hs]);
   float mrun[HPW][2], lrun[HPW][2];
 #pragma unroll
   for (int hs = 0; hs < HPW; ++hs)
@@ -438,9 +440,8 @@ __global__ void __launch_bounds__(WM_THREADS) window_attn_mma_kernel(WaParams P,
     for (int hs = 0; hs < HPW; ++hs) {
       const int h = warp + hs * WM_WARPS;
       if (h < P.H) {
-        if (HPW > 1) wm_load_q(P, tl, h, lane, qf[0]);
         float s[4][4];
-        wm_scores(P, tl, u0, h, lane, qf[0], Ks, kpitch, qpos, s);
+        wm_scores(P, tl, u0, h, lane, qf[hs], Ks, kpitch, qpos, s);
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           float mx = -INFINITY;
@@ -491,9 +492,8 @@ __global__ void __launch_bounds__(WM_THREADS) window_attn_mma_kernel(WaParams P,
       for (int hs = 0; hs < HPW; ++hs) {
         const int h = warp + hs * WM_WARPS;
         if (h < P.H) {
-          if (HPW > 1) wm_load_q(P, tl, h, lane, qf[0]);
           float s[4][4];
-          wm_scores(P, tl, u0, h, lane, qf[0], Ks, kpitch, qpos, s);
+          wm_scores(P, tl, u0, h, lane, qf[hs], Ks, kpitch, qpos, s);
 #pragma unroll
           for (int nt = 0; nt < 4; ++nt)
 #pragma unroll

@@ -77,7 +77,7 @@ def test_short_conv_long_prompt_many_time_tiles():
 
 
 # ------------------------------------------------------------------ recurrence
-@pytest.mark.parametrize("H,G,n,p", [(3, 1, 10, 8), (4, 2, 48, 32), (2, 2, 16, 5), (1, 1, 1, 1), (2, 1, 130, 3), (6, 6, 32, 64)])
+@pytest.mark.parametrize("H,G,n,p", [(3, 1, 10, 8), (4, 2, 48, 32), (2, 2, 16, 5), (1, 1, 1, 1), (2, 1, 130, 3), (6, 6, 32, 64), (2, 1, 300, 3), (2, 2, 128, 16)])
 @pytest.mark.parametrize("per_channel", [False, True])
 def test_decay_scan_in_portions(H, G, n, p, per_channel):
     from lit_llama.recurrence import decay_scan

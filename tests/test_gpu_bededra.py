@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from oracle import bededra as O
-from tests.util_bededra import TOL32, agrees, case_mixed, case_odd, case_ones, load, rel_err, run_schedule, write_model
+from tests.util_bededra import TOL32, agrees, case_mixed, case_odd, case_one_kind, case_ones, load, rel_err, run_schedule, write_model
 
 pytestmark = pytest.mark.gpu
 
@@ -110,6 +110,19 @@ def test_sizes_that_are_odd(odd, dtype):
     m = load(folder, dtype)
     for portions in ([len(toks)], [9] + [1] * 22, [2, 3, 5, 7, 11, 3]):
         got = run_schedule(m, toks, portions, 32)[0]
+        assert agrees(got, want, dtype), rel_err(got, want)
+
+
+@pytest.mark.parametrize("kind", ["mamba2", "parallel"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_models_of_one_kind_of_mixer(tmp_path, kind, dtype):
+    cfg, W = case_one_kind(kind)
+    folder = write_model(tmp_path / kind, cfg, W)
+    toks = np.random.RandomState(13).randint(0, cfg["vocab"], size=37).tolist()
+    want = O.forward(cfg, W, toks)
+    m = load(folder, dtype)
+    for portions in ([37], [20] + [1] * 17, [2, 9, 1, 25]):
+        got = run_schedule(m, toks, portions, 48)[0]
         assert agrees(got, want, dtype), rel_err(got, want)
 
 

@@ -145,6 +145,19 @@ def case_odd(seed=2):
     return cfg, random_weights(cfg, seed)
 
 
+def case_one_kind(kind, seed=3):
+    """Models with a single kind of mixer (no key/value rows at all, or no state-space layer), unbounded window."""
+    if kind == "mamba2":
+        layers = [(mamba(2, 8, 12, groups=2, norm_groups=2), dense(20)), (mamba(4, 4, 6), None)]
+    else:
+        p1 = parallel(2, 2, 16, 16, window=9, keep=4, r_heads=2, r_dim=8, r_vdim=8)
+        p2 = parallel(4, 1, 8, 8, window=9, keep=0, r_heads=1, r_dim=16, r_vdim=16, softcap=0.0)
+        p2["mixer"]["left"]["mask"] = {}                      # no window, nothing kept: every earlier token is visible
+        layers = [(p1, moe(4, 2, 8, count=2, keep=1)), (p2, dense(16))]
+    cfg = model_cfg(29, 24, layers, eps=1e-5, taps=4)
+    return cfg, random_weights(cfg, seed)
+
+
 def write_model(folder, cfg, W):
     from lit_llama.safetensors_io import save_safetensors
 

@@ -90,8 +90,6 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
     }
     __syncthreads();
     if (t0 + DS_TC < Tn) fetch(t0 + DS_TC);
-    // unrolled so that a token's shared-memory reads run under the previous token's arithmetic
-#pragma unroll 4
     for (int tt = 0; tt < nt; ++tt) {
       const float vv = s_v[tt][pl];
       float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;

@@ -212,6 +212,22 @@ def test_window_attention_on_a_wrapping_ring(H, G, D, V, window, keep, dtype):
         close(got, attention_want(att, proj, params, dtype), TOL[dtype] * 2)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_window_attention_over_many_chunks(dtype):
+    """A window of 100 keys beside 7 kept tokens over 300 tokens: every query tile walks several staged chunks, the ring
+    (window - 1 + 64 slots) wraps twice, and the last tokens are decoded alone with the window split over blocks."""
+    H, G, D, V, window, keep, T = 8, 2, 32, 32, 100, 7, 300
+    att, caches, params = attention_setup(H, G, D, V, window, keep, window - 1 + 64, dtype, cap=25.0, seed=3)
+    proj = np.random.RandomState(4).randn(T, att.n_in)
+    want = attention_want(att, proj, params, dtype)
+    for portions, splits in (([64] * 4 + [44], 1), ([50, 64, 64, 64, 40] + [1] * 18, 4)):
+        out, at = [], 0
+        for n in portions:
+            out.append(att(dev(proj[at:at + n], dtype), 0, 1, n, pos(at, at + n), caches, splits if n == 1 else 1))
+            at += n
+        close(torch.cat(out), want, TOL[dtype] * 2)
+
+
 @pytest.mark.parametrize("splits", [1, 3, 16])
 def test_one_key_that_takes_the_weight_at_every_edge(splits):
     """Query i and one key j* share a large component, so j* takes nearly all of the weight when it is visible: j* just

@@ -20,7 +20,8 @@ __host__ __device__ constexpr int ds_tc(int npad) { return npad <= 64 ? 16 : npa
 // columns per block.  A thread's rows are interleaved in quads, row(k, e) = (k * NP + part) * 4 + e, so that the NP lanes of
 // a column read consecutive 16-byte units of the staged token (no bank conflicts).
 // DS_NL: state rows a thread keeps in registers (8: more threads per head, the usual case; 16: heads of more than 256 rows).
-template <typename T, int NP, int DS_NL>
+// PERCH: a decay per state row (gated linear attention); otherwise one per head and token, read once per token.
+template <typename T, int NP, int DS_NL, bool PERCH>
 __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
     const T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride, const T* __restrict__ v, int v_stride,
     const float* __restrict__ a, int a_per_channel, const float* __restrict__ ks, const float* __restrict__ skip, float qs,
@@ -94,9 +95,11 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
       const float vv = s_v[tt][pl];
       float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
 #pragma unroll
+      const float a1 = s_a[tt][0];
+#pragma unroll
       for (int i4 = 0; i4 < DS_NL; i4 += 4) {
         const int at = ((i4 >> 2) * NP + part) * 4;
-        const float4 a4 = *(const float4*)&s_a[tt][at];
+        const float4 a4 = PERCH ? *(const float4*)&s_a[tt][at] : make_float4(a1, a1, a1, a1);
         const float4 k4 = *(const float4*)&s_k[tt][at];
         const float4 q4 = *(const float4*)&s_q[tt][at];
         S[i4 + 0] = a4.x * S[i4 + 0] + k4.x * vv;
@@ -127,9 +130,13 @@ static int decay_scan_launch(const void* q, int q_stride, const void* k, int k_s
                              int a_per_channel, const float* ks, const float* skip, float qs, float* state, const int32_t* pos_ids,
                              float* y, int B, int Tn, int H, int qk_heads, int n, int p, cudaStream_t st) {
   constexpr int PT = DS_THREADS / NP;
-  decay_scan_kernel<T, NP, NL><<<dim3((p + PT - 1) / PT, H, B), DS_THREADS, 0, st>>>((const T*)q, q_stride, (const T*)k, k_stride,
-                                                                                (const T*)v, v_stride, a, a_per_channel, ks, skip,
-                                                                                qs, state, pos_ids, y, Tn, H, qk_heads, n, p);
+  const dim3 grid((p + PT - 1) / PT, H, B);
+  if (a_per_channel)
+    decay_scan_kernel<T, NP, NL, true><<<grid, DS_THREADS, 0, st>>>((const T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, a, 1,
+                                                                    ks, skip, qs, state, pos_ids, y, Tn, H, qk_heads, n, p);
+  else
+    decay_scan_kernel<T, NP, NL, false><<<grid, DS_THREADS, 0, st>>>((const T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, a, 0,
+                                                                     ks, skip, qs, state, pos_ids, y, Tn, H, qk_heads, n, p);
   LL_LAUNCH_OK("decay_scan_kernel");
   return LL_OK;
 }

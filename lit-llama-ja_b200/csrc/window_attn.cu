@@ -312,6 +312,12 @@ struct WmTile { int b, t0, rows, i_first, i_last, ns, w0, n_list; };
 
 __device__ __forceinline__ int wm_key(const WmTile& tl, int u) { return u < tl.ns ? u : tl.w0 + (u - tl.ns); }
 
+// A chunk of the window part that lies before every query of a full tile and inside every query's window
+__device__ __forceinline__ bool wm_interior(const WaParams& P, const WmTile& tl, int u0, int jf) {
+  return tl.rows == WM_Q && tl.i_last - tl.i_first == WM_Q - 1 && u0 >= tl.ns && u0 + WM_KC <= tl.n_list &&
+         jf + WM_KC - 1 <= tl.i_first && tl.i_last - jf < P.window;
+}
+
 // A fragments of one head's 16 x dim query tile, straight from the projection's rows
 __device__ __forceinline__ void wm_load_q(const WaParams& P, const WmTile& tl, int h, int lane, uint32_t (&qf)[WM_DK_MAX][4]) {
   const __nv_bfloat16* q = (const __nv_bfloat16*)P.q;
@@ -351,8 +357,10 @@ __device__ __forceinline__ void wm_stage(const WaParams& P, const WmTile& tl, in
 }
 
 // S[16 x 32] of head h against the staged chunk, then cap, distance penalty and mask (-inf where not visible)
+// interior: every key of the chunk (positions jf .. jf + 31) is visible to every query of the tile - no mask to evaluate
 __device__ __forceinline__ void wm_scores(const WaParams& P, const WmTile& tl, int u0, int h, int lane, const uint32_t (&qf)[WM_DK_MAX][4],
-                                          const __nv_bfloat16* Ks, int kpitch, const int (&qpos)[2], float (&s)[4][4]) {
+                                          const __nv_bfloat16* Ks, int kpitch, const int (&qpos)[2], bool interior, int jf,
+                                          float (&s)[4][4]) {
   const int g = h / (P.H / P.G), dk = P.dim / 16;
 #pragma unroll
   for (int nt = 0; nt < 4; ++nt)
@@ -376,12 +384,13 @@ __device__ __forceinline__ void wm_scores(const WaParams& P, const WmTile& tl, i
   for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const int u = u0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+      const int col = nt * 8 + (lane & 3) * 2 + (e & 1);
+      const int u = u0 + col;
       const int i = qpos[e >> 1];
       float v = -INFINITY;
-      if (u < tl.n_list && i >= 0) {
-        const int j = wm_key(tl, u);
-        if (j <= i && (i - j < P.window || j < P.keep)) {
+      if (interior || (u < tl.n_list && i >= 0)) {
+        const int j = interior ? jf + col : wm_key(tl, u);
+        if (interior || (j <= i && (i - j < P.window || j < P.keep))) {
           v = s[nt][e] * P.scale;
           if (P.cap > 0.f) {                                        // cap * tanh(v / cap), tanh(x) = 1 - 2 / (exp(2x) + 1)
             const float ex = __expf(2.f * v * inv_cap);
@@ -395,7 +404,7 @@ __device__ __forceinline__ void wm_scores(const WaParams& P, const WmTile& tl, i
 }
 
 template <int HPW>
-__global__ void __launch_bounds__(WM_THREADS) window_attn_mma_kernel(WaParams P, const __nv_bfloat16* __restrict__ gate,
+__global__ void __launch_bounds__(WM_THREADS, 1) window_attn_mma_kernel(WaParams P, const __nv_bfloat16* __restrict__ gate,
                                                                      int gate_stride, __nv_bfloat16* __restrict__ y) {
   extern __shared__ __align__(16) unsigned char wm_smem[];
   const int Hp = (P.H + 15) / 16 * 16;
@@ -436,12 +445,14 @@ __global__ void __launch_bounds__(WM_THREADS) window_attn_mma_kernel(WaParams P,
   // ---- sweep 1: maximum and sum of every (head, query)
   for (int u0 = 0; u0 < tl.n_list; u0 += WM_KC) {
     wm_stage(P, tl, u0, Ks, kpitch, Vs, vpitch, false);
+    const int jf = wm_key(tl, u0);
+    const bool interior = wm_interior(P, tl, u0, jf);
 #pragma unroll
     for (int hs = 0; hs < HPW; ++hs) {
       const int h = warp + hs * WM_WARPS;
       if (h < P.H) {
         float s[4][4];
-        wm_scores(P, tl, u0, h, lane, qf[hs], Ks, kpitch, qpos, s);
+        wm_scores(P, tl, u0, h, lane, qf[hs], Ks, kpitch, qpos, interior, jf, s);
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           float mx = -INFINITY;
@@ -488,12 +499,14 @@ __global__ void __launch_bounds__(WM_THREADS) window_attn_mma_kernel(WaParams P,
       for (int e = 0; e < 4; ++e) o[nt][e] = 0.f;
     for (int u0 = 0; u0 < tl.n_list; u0 += WM_KC) {
       wm_stage(P, tl, u0, Ks, kpitch, Vs, vpitch, true);
+      const int jf = wm_key(tl, u0);
+      const bool interior = wm_interior(P, tl, u0, jf);
 #pragma unroll
       for (int hs = 0; hs < HPW; ++hs) {
         const int h = warp + hs * WM_WARPS;
         if (h < P.H) {
           float s[4][4];
-          wm_scores(P, tl, u0, h, lane, qf[hs], Ks, kpitch, qpos, s);
+          wm_scores(P, tl, u0, h, lane, qf[hs], Ks, kpitch, qpos, interior, jf, s);
 #pragma unroll
           for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
